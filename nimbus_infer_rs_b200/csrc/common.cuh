@@ -18,7 +18,8 @@ enum NbDType : int { NB_F32 = 0, NB_BF16 = 1 };
 // Activation applied in a matrix product's epilogue.
 enum NbAct : int { NB_ACT_NONE = 0, NB_ACT_GELU_TANH = 1, NB_ACT_GELU_ERF = 2, NB_ACT_SILU = 3,
                    NB_ACT_RELU2 = 4,   // the square of relu
-                   NB_ACT_TANH = 5, NB_ACT_XIELU = 6 };   // row passes only (nb_act_rows)
+                   NB_ACT_TANH = 5, NB_ACT_XIELU = 6,     // row passes only (nb_act_rows)
+                   NB_ACT_RELU = 7 };                     // row passes and gates (nb_glu_rows)
 
 // Error codes above the range of cudaError_t.
 #define NB_ERR_BAD_ARG 10001
@@ -202,6 +203,7 @@ __device__ __forceinline__ float nb_apply_act_fast(float x, int act) {
   if (act == NB_ACT_GELU_ERF) return nb_gelu_erf(x);
   if (act == NB_ACT_SILU) return nb_silu_fast(x);
   if (act == NB_ACT_RELU2) return x > 0.0f ? x * x : 0.0f;
+  if (act == NB_ACT_RELU) return fmaxf(x, 0.0f);
   return x;
 }
 __device__ __forceinline__ float nb_apply_act(float x, int act) {
@@ -209,6 +211,7 @@ __device__ __forceinline__ float nb_apply_act(float x, int act) {
   if (act == NB_ACT_GELU_ERF) return nb_gelu_erf(x);
   if (act == NB_ACT_SILU) return nb_silu(x);
   if (act == NB_ACT_RELU2) return x > 0.0f ? x * x : 0.0f;
+  if (act == NB_ACT_RELU) return fmaxf(x, 0.0f);
   return x;
 }
 

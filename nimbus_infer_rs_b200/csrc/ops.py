@@ -15,10 +15,13 @@ import os
 import torch
 
 ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU, ACT_RELU2, ACT_TANH, ACT_XIELU = 0, 1, 2, 3, 4, 5, 6
+ACT_RELU = 7
 # what a dense product's epilogue can apply
 ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GELU_ERF}
 # what the experts' first product (routed experts) can apply
 GATE_ACTIVATIONS = {**ACTIVATIONS, "silu": ACT_SILU, "relu2": ACT_RELU2}
+# what the gate of a gated dense feed-forward can apply (`glu_rows`)
+GLU_ACTIVATIONS = {**GATE_ACTIVATIONS, "relu": ACT_RELU}
 # what a pass over fp32 rows can apply (`act_rows`): those, and activations with learned numbers
 ROW_ACTIVATIONS = {"tanh": ACT_TANH, "xielu": ACT_XIELU}
 
@@ -713,6 +716,187 @@ class CudaBackend:
                    _ptr(state), _ptr(o_raw), _ptr(out), dtype_code(out.dtype), n_heads, dim,
                    layout.n_seqs, n, self._stream())
         self.launches += 1
+
+    # -- short convolutions, capped attention, linear recurrences ------------------------
+    @staticmethod
+    def _state_rows(state, n):
+        """A mixer's part of the fixed-size state rows: fp32 ``[n_slots, n]``, rows ``stride(0)``
+        floats apart (a view of some columns of the cache's rows)."""
+        if state is None:
+            return None
+        if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or \
+                state.shape[1] != n:
+            raise KernelError(f"state rows: expected fp32 [slots, {n}] with unit column stride")
+        return state
+
+    def conv_rope_append(self, src, col0, w, taps, state, freq, rot_dims, layout, k_store,
+                         v_store, n_heads, dv, q_out):
+        """The short causal convolution (``w`` fp32 ``[channels, taps]``, or ``None`` for none)
+        on the channels ``[queries | keys | values]`` of the fp32 rows ``src`` from column
+        ``col0``, then the rotation by position of the queries' and keys' first ``rot_dims``
+        numbers per head (neighbouring numbers paired); queries to ``q_out``, keys and values
+        into the paged stores.  ``state``: the sequences' last ``taps - 1`` inputs, brought up
+        to date for the next step."""
+        _check(src, "src", torch.float32, 2)
+        _check(q_out, "q_out", None, 2)
+        d, G = k_store.head_dim, k_store.n_kv_heads
+        C = n_heads * d + G * d + G * dv
+        n = layout.n_rows
+        taps = int(taps) if w is not None else 0
+        if q_out.shape != (n, n_heads * d) or src.shape[0] < n or src.shape[1] < col0 + C or \
+                v_store.head_dim != dv or v_store.n_kv_heads != G or \
+                (w is not None and tuple(w.shape) != (C, taps)) or \
+                (rot_dims and (freq is None or freq.numel() != rot_dims // 2)):
+            raise KernelError("conv_rope_append: shapes do not agree")
+        st = self._state_rows(state, (taps - 1) * C) if taps > 1 else None
+        fused = 1 if layout.is_decode and layout.max_q_len == 1 else 0
+        self._call("nb_conv_rope_append", _ptr(src), src.shape[1], col0, _ptr(w), taps, _ptr(st),
+                   st.stride(0) if st is not None else 0, _ptr(layout.cu_rows),
+                   _ptr(layout.seq_slot), _ptr(layout.seq_pos0), _ptr(freq), int(rot_dims),
+                   _ptr(q_out), dtype_code(q_out.dtype), _ptr(k_store.k), _ptr(k_store.block_table),
+                   k_store.block_table.shape[1], _ptr(v_store.k), _ptr(v_store.block_table),
+                   v_store.block_table.shape[1], dtype_code(k_store.k.dtype), k_store.page, n_heads,
+                   G, d, dv, layout.n_seqs, layout.max_q_len, fused, self._stream())
+        if taps > 1 and not fused:
+            self._call("nb_conv_state_update", _ptr(src), src.shape[1], col0, taps, _ptr(st),
+                       st.stride(0), _ptr(layout.cu_rows), _ptr(layout.seq_slot), C, layout.n_seqs,
+                       self._stream())
+
+    def conv_act(self, src, col0, w, bias, taps, act, state, layout, out_f32, out_act=None):
+        """``out_f32 = act(conv(src[:, col0 : col0 + C]) + bias)`` per channel over time, the
+        sequences' last ``taps - 1`` inputs kept in ``state``; ``out_act``: the same rows in the
+        activation type (the next product's operand)."""
+        _check(src, "src", torch.float32, 2)
+        _check(out_f32, "out_f32", torch.float32, 2)
+        n, C = out_f32.shape
+        taps = int(taps) if w is not None else 0
+        if n != layout.n_rows or src.shape[0] < n or src.shape[1] < col0 + C or \
+                (w is not None and tuple(w.shape) != (C, taps)) or \
+                (bias is not None and bias.numel() != C) or \
+                (out_act is not None and out_act.shape != out_f32.shape):
+            raise KernelError("conv_act: shapes do not agree")
+        st = self._state_rows(state, (taps - 1) * C) if taps > 1 else None
+        fused = 1 if layout.is_decode and layout.max_q_len == 1 else 0
+        if out_act is not None and out_act.dtype == torch.float32:
+            out_act = None          # the 32-bit rows are the operand
+        self._call("nb_conv_act", _ptr(src), src.shape[1], col0, _ptr(w), _ptr(bias), taps, int(act),
+                   _ptr(st), st.stride(0) if st is not None else 0, _ptr(layout.cu_rows),
+                   _ptr(layout.seq_slot), C, _ptr(out_f32), _ptr(out_act),
+                   dtype_code(out_act.dtype) if out_act is not None else 0, layout.n_seqs,
+                   layout.max_q_len, fused, self._stream())
+        if taps > 1 and not fused:
+            self._call("nb_conv_state_update", _ptr(src), src.shape[1], col0, taps, _ptr(st),
+                       st.stride(0), _ptr(layout.cu_rows), _ptr(layout.seq_slot), C, layout.n_seqs,
+                       self._stream())
+
+    def attention_capped(self, q, layout, k_store, v_store, n_heads, sink, out, scale, softcap):
+        """Causal attention of the packed rows over the keys of ``k_store`` and the values of
+        ``v_store`` (paged stores of one plane, head sizes ``d`` and ``dv``): scores ``scale *
+        q . k``, with ``softcap`` > 0 replaced by ``softcap * tanh(score / softcap)``; ``sink``:
+        fp32 ``[n_heads]`` logits of one more term of the softmax's denominator, or ``None``."""
+        _check(q, "q", None, 2)
+        _check(out, "out", None, 2)
+        n, d, dv = layout.n_rows, k_store.head_dim, v_store.head_dim
+        if q.shape != (n, n_heads * d) or out.shape != (n, n_heads * dv) or \
+                k_store.n_kv_heads != v_store.n_kv_heads or k_store.k.dtype != v_store.k.dtype:
+            raise KernelError("attention_capped: shapes do not agree")
+        if sink is not None:
+            _check(sink, "sink", torch.float32, 1)
+            if sink.numel() != n_heads:
+                raise KernelError("attention_capped: one sink per head")
+        self._call("nb_attention_capped", _ptr(q), dtype_code(q.dtype), _ptr(layout.row_slot),
+                   _ptr(layout.row_pos), _ptr(k_store.k), _ptr(k_store.block_table),
+                   k_store.block_table.shape[1], _ptr(v_store.k), _ptr(v_store.block_table),
+                   v_store.block_table.shape[1], dtype_code(k_store.k.dtype), k_store.page, n_heads,
+                   k_store.n_kv_heads, d, dv, _ptr(sink), _ptr(out), dtype_code(out.dtype),
+                   float(scale), float(softcap or 0.0), n, self._stream())
+
+    def selective_scan(self, x, low, col_b, col_c, dt_lin, dt_bias, a_log, d_skip, z, z_col, state,
+                       layout, n_state, out):
+        """The selective scan over each sequence's rows in order, from and into the sequences'
+        state rows (``[slots, inner * n_state]``): ``x`` the channels' inputs, ``low`` the rows
+        holding B and C at columns ``col_b`` / ``col_c``, ``dt_lin`` the step sizes before bias
+        and softplus, ``z`` (columns ``z_col ..``) the gates; all fp32."""
+        for t, nm in ((x, "x"), (low, "low"), (dt_lin, "dt_lin"), (z, "z")):
+            _check(t, nm, torch.float32, 2)
+        _check(out, "out", None, 2)
+        n, inner = layout.n_rows, x.shape[1]
+        if out.shape != (n, inner) or dt_lin.shape != (n, inner) or x.shape[0] != n or \
+                low.shape[1] < max(col_b, col_c) + n_state or z.shape[1] < z_col + inner or \
+                dt_bias.numel() != inner or d_skip.numel() != inner or \
+                tuple(a_log.shape) != (inner, n_state):
+            raise KernelError("selective_scan: shapes do not agree")
+        st = self._state_rows(state, inner * n_state)
+        self._call("nb_selective_scan", _ptr(x), _ptr(low), low.shape[1], col_b, col_c, _ptr(dt_lin),
+                   _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(z), z.shape[1], z_col, _ptr(st),
+                   st.stride(0), _ptr(layout.cu_rows), _ptr(layout.seq_slot), inner, int(n_state),
+                   _ptr(out), dtype_code(out.dtype), layout.n_seqs, self._stream())
+
+    def linear_attention(self, fused, col_q, col_k, col_v, act, decay, state, layout, n_heads, d, dv,
+                         out):
+        """Per head ``S <- decay_h S + k v^T``, ``o = S^T q`` over each sequence's rows in order
+        (``q, k, v`` = ``act`` of the columns of the fp32 rows ``fused``), from and into the
+        state rows (``[slots, n_heads * d * dv]``); ``out``: fp32 ``[rows, n_heads * dv]``."""
+        _check(fused, "fused", torch.float32, 2)
+        _check(out, "out", torch.float32, 2)
+        _check(decay, "decay", torch.float32, 1)
+        n = layout.n_rows
+        if out.shape != (n, n_heads * dv) or decay.numel() != n_heads or fused.shape[0] < n or \
+                fused.shape[1] < max(col_q + n_heads * d, col_k + n_heads * d, col_v + n_heads * dv):
+            raise KernelError("linear_attention: shapes do not agree")
+        st = self._state_rows(state, n_heads * d * dv)
+        self._call("nb_linear_attention", _ptr(fused), fused.shape[1], col_q, col_k, col_v, int(act),
+                   _ptr(decay), _ptr(st), st.stride(0), _ptr(layout.cu_rows), _ptr(layout.seq_slot),
+                   n_heads, d, dv, _ptr(out), layout.n_seqs, self._stream())
+
+    def rmsnorm_gated(self, x, gamma, gate, gate_col, eps, out):
+        """``out = x / sqrt(mean(x^2) + eps) * gamma * sigmoid(gate[:, gate_col : gate_col + d])``
+        per fp32 row."""
+        _check(x, "x", torch.float32, 2)
+        _check(gate, "gate", torch.float32, 2)
+        _check(gamma, "gamma", torch.float32, 1)
+        _check(out, "out", None, 2)
+        n, d = out.shape
+        if x.shape != (n, d) or gamma.numel() != d or gate.shape[0] < n or gate.shape[1] < gate_col + d:
+            raise KernelError("rmsnorm_gated: shapes do not agree")
+        self._call("nb_rmsnorm_gated", _ptr(x), _ptr(gamma), _ptr(gate), gate.shape[1], gate_col,
+                   _ptr(out), dtype_code(out.dtype), n, d, float(eps), self._stream())
+
+    def rms_pair_add(self, a, gamma_a, b, gamma_b, eps, coef, residual, next_gamma=None,
+                     next_eps=0.0, out_next=None):
+        """``residual += coef * (rms-norm(a) * gamma_a + rms-norm(b) * gamma_b)`` per fp32 row,
+        and in the same pass, where asked for, ``out_next = rms-norm(residual) * next_gamma``."""
+        for t, nm in ((a, "a"), (b, "b"), (residual, "residual")):
+            _check(t, nm, torch.float32, 2)
+        n, d = residual.shape
+        if a.shape != (n, d) or b.shape != (n, d) or gamma_a.numel() != d or gamma_b.numel() != d \
+                or (out_next is not None and (out_next.shape != (n, d) or next_gamma is None
+                                              or next_gamma.numel() != d)):
+            raise KernelError("rms_pair_add: shapes do not agree")
+        self._call("nb_rms_pair_add", _ptr(a), _ptr(gamma_a), _ptr(b), _ptr(gamma_b), float(eps),
+                   float(coef), _ptr(residual), _ptr(next_gamma if out_next is not None else None),
+                   float(next_eps), _ptr(out_next),
+                   dtype_code(out_next.dtype) if out_next is not None else 0, n, d, self._stream())
+
+    def glu_rows(self, x, gate_col, up_col, act, out):
+        """``out[r, i] = act(x[r, gate_col + i]) * x[r, up_col + i]`` for fp32 rows ``x``."""
+        _check(x, "x", torch.float32, 2)
+        _check(out, "out", None, 2)
+        n, d = out.shape
+        if x.shape[0] < n or x.shape[1] < max(gate_col, up_col) + d:
+            raise KernelError("glu_rows: shapes do not agree")
+        self._call("nb_glu_rows", _ptr(x), x.shape[1], gate_col, up_col, int(act), _ptr(out),
+                   dtype_code(out.dtype), n, d, self._stream())
+
+    def cast_cols(self, x, out, out_col):
+        """``out[:, out_col : out_col + d] = x`` (fp32 rows into columns of rows of another type)."""
+        _check(x, "x", torch.float32, 2)
+        _check(out, "out", None, 2)
+        n, d = x.shape
+        if out.shape[0] != n or out.shape[1] < out_col + d:
+            raise KernelError("cast_cols: shapes do not agree")
+        self._call("nb_cast_cols", _ptr(x), _ptr(out), dtype_code(out.dtype), out.shape[1], out_col,
+                   n, d, self._stream())
 
     # -- routed experts ---------------------------------------------------------------
     def moe_route(self, logits, col, n_experts, top, renormalize, layout, idx, weight):

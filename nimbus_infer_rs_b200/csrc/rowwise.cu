@@ -614,6 +614,186 @@ NB_EXPORT int nb_gather_mul(const float* g, const void* table, int table_dtype, 
 }
 
 // ---------------------------------------------------------------------------------
+// out[r, i] = act(x[r, gate_col + i]) * x[r, up_col + i]: the gated half of a feed-forward whose
+// two first products come side by side in one fp32 row.
+// ---------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void glu_rows_kernel(const float* x, int x_stride, int gate_col, int up_col, int act,
+                                TOut* out, int d, size_t total) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = e / d;
+    const int i = (int)(e - r * d);
+    const float* row = x + r * x_stride;
+    out[e] = nb_from_f32<TOut>(nb_apply_act(row[gate_col + i], act) * row[up_col + i]);
+  }
+}
+
+NB_EXPORT int nb_glu_rows(const float* x, int x_stride, int gate_col, int up_col, int act, void* out,
+                          int out_dtype, int n_rows, int d, cudaStream_t stream) {
+  if (n_rows == 0 || d == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && d > 0 && gate_col >= 0 && up_col >= 0 && x_stride >= gate_col + d &&
+                 x_stride >= up_col + d,
+             NB_ERR_BAD_ARG, "glu_rows: bad sizes rows=%d d=%d cols=%d/%d stride=%d", n_rows, d,
+             gate_col, up_col, x_stride);
+  const size_t total = (size_t)n_rows * d;
+  const int blocks = (int)((total + 1023) / 1024 < 148 * 8 ? (total + 1023) / 1024 : 148 * 8);
+  if (out_dtype == NB_F32)
+    NB_CUDA(nb_launch(glu_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, x_stride,
+                      gate_col, up_col, act, (float*)out, d, total));
+  else if (out_dtype == NB_BF16)
+    NB_CUDA(nb_launch(glu_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, x,
+                      x_stride, gate_col, up_col, act, (__nv_bfloat16*)out, d, total));
+  else
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "glu_rows: unknown output dtype %d", out_dtype);
+  NB_CHECK_LAUNCH("glu_rows");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// out[r, out_col + i] = x[r, i] for fp32 rows x, into rows of stride out_stride of another type:
+// the stream as the operand of a product, written beside other columns of the same operand.
+// ---------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void cast_cols_kernel(const float* x, TOut* out, int out_stride, int out_col, int d,
+                                 size_t total) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+       e += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = e / d;
+    const int i = (int)(e - r * d);
+    out[r * out_stride + out_col + i] = nb_from_f32<TOut>(x[e]);
+  }
+}
+
+NB_EXPORT int nb_cast_cols(const float* x, void* out, int out_dtype, int out_stride, int out_col,
+                           int n_rows, int d, cudaStream_t stream) {
+  if (n_rows == 0 || d == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && d > 0 && out_col >= 0 && out_stride >= out_col + d, NB_ERR_BAD_ARG,
+             "cast_cols: bad sizes rows=%d d=%d col=%d stride=%d", n_rows, d, out_col, out_stride);
+  const size_t total = (size_t)n_rows * d;
+  const int blocks = (int)((total + 1023) / 1024 < 148 * 8 ? (total + 1023) / 1024 : 148 * 8);
+  if (out_dtype == NB_F32)
+    NB_CUDA(nb_launch(cast_cols_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (float*)out,
+                      out_stride, out_col, d, total));
+  else if (out_dtype == NB_BF16)
+    NB_CUDA(nb_launch(cast_cols_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, x,
+                      (__nv_bfloat16*)out, out_stride, out_col, d, total));
+  else
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "cast_cols: unknown output dtype %d", out_dtype);
+  NB_CHECK_LAUNCH("cast_cols");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// RMS norm of a whole fp32 row times a weight and a gate:
+//   out[r, i] = x[r, i] / sqrt(mean(x[r]^2) + eps) * gamma[i] * sigmoid(g[r, g_col + i])
+// (heads side by side normed together, then gated by a projection of the same input).
+// ---------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void rmsnorm_gated_kernel(const float* x, const float* __restrict__ gamma,
+                                     const float* g, int g_stride, int g_col, TOut* out, int d,
+                                     float eps) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)r * d;
+  const float* gr = g + (size_t)r * g_stride + g_col;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = xr[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = nb_block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x)
+    out[(size_t)r * d + i] = nb_from_f32<TOut>(xr[i] * inv * gamma[i] * nb_sigmoid(gr[i]));
+}
+
+NB_EXPORT int nb_rmsnorm_gated(const float* x, const float* gamma, const float* g, int g_stride,
+                               int g_col, void* out, int out_dtype, int n_rows, int d, float eps,
+                               cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && d > 0 && g_col >= 0 && g_stride >= g_col + d, NB_ERR_BAD_ARG,
+             "rmsnorm_gated: bad sizes rows=%d d=%d col=%d stride=%d", n_rows, d, g_col, g_stride);
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : (d >= 128 ? 128 : 64));
+  if (out_dtype == NB_F32)
+    NB_CUDA(nb_launch(rmsnorm_gated_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, gamma,
+                      g, g_stride, g_col, (float*)out, d, eps));
+  else if (out_dtype == NB_BF16)
+    NB_CUDA(nb_launch(rmsnorm_gated_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream,
+                      x, gamma, g, g_stride, g_col, (__nv_bfloat16*)out, d, eps));
+  else
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "rmsnorm_gated: unknown output dtype %d", out_dtype);
+  NB_CHECK_LAUNCH("rmsnorm_gated");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// Two sublayers' results, each RMS-normed over the row with a weight of its own, averaged into
+// the stream, and (optionally) the norm in front of the stream's next reader in the same pass:
+//   x[r] += coef * (a[r] / rms(a[r]) * gamma_a + b[r] / rms(b[r]) * gamma_b)       (fp32)
+//   out_next[r] = x[r] / sqrt(mean(x[r]^2) + next_eps) * next_gamma    if out_next  (TOut)
+// ---------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void rms_pair_add_kernel(const float* a, const float* __restrict__ gamma_a,
+                                    const float* b, const float* __restrict__ gamma_b, float eps,
+                                    float coef, float* x, const float* __restrict__ next_gamma,
+                                    float next_eps, TOut* out_next, int d) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const float* ar = a + (size_t)r * d;
+  const float* br = b + (size_t)r * d;
+  float* xr = x + (size_t)r * d;
+  float sa = 0.0f, sb = 0.0f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    sa = fmaf(ar[i], ar[i], sa);
+    sb = fmaf(br[i], br[i], sb);
+  }
+  sa = nb_block_sum(sa, red);
+  sb = nb_block_sum(sb, red);
+  const float ia = 1.0f / sqrtf(sa / (float)d + eps), ib = 1.0f / sqrtf(sb / (float)d + eps);
+  float sx = 0.0f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float v = xr[i] + coef * (ar[i] * ia * gamma_a[i] + br[i] * ib * gamma_b[i]);
+    xr[i] = v;
+    sx = fmaf(v, v, sx);
+  }
+  if (out_next == nullptr) return;
+  sx = nb_block_sum(sx, red);
+  const float ix = 1.0f / sqrtf(sx / (float)d + next_eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x)
+    out_next[(size_t)r * d + i] = nb_from_f32<TOut>(xr[i] * ix * next_gamma[i]);
+}
+
+NB_EXPORT int nb_rms_pair_add(const float* a, const float* gamma_a, const float* b,
+                              const float* gamma_b, float eps, float coef, float* x,
+                              const float* next_gamma, float next_eps, void* out_next,
+                              int out_dtype, int n_rows, int d, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && d > 0 && (out_next == nullptr || next_gamma != nullptr), NB_ERR_BAD_ARG,
+             "rms_pair_add: bad sizes rows=%d d=%d", n_rows, d);
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : (d >= 128 ? 128 : 64));
+  if (out_next == nullptr || out_dtype == NB_F32)
+    NB_CUDA(nb_launch(rms_pair_add_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, a,
+                      gamma_a, b, gamma_b, eps, coef, x, next_gamma, next_eps, (float*)out_next, d));
+  else if (out_dtype == NB_BF16)
+    NB_CUDA(nb_launch(rms_pair_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, a,
+                      gamma_a, b, gamma_b, eps, coef, x, next_gamma, next_eps,
+                      (__nv_bfloat16*)out_next, d));
+  else
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "rms_pair_add: unknown output dtype %d", out_dtype);
+  NB_CHECK_LAUNCH("rms_pair_add");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
 // Append this step's keys and values to the paged cache (src/cache.rs:44-57 writes rows
 // P..P+T of every head).  Row r of `src` holds [.. | K: n_kv_heads*head_dim | V: same ..]
 // starting at column k_col / v_col; it goes to token `pos[r]` of sequence slot `slot[r]`.

@@ -57,6 +57,18 @@ SIGNATURES = {
     "nb_pool_blocks": "pppppipppiiiiiiip",
     "nb_attention_pooled_mma": "piippppppipppiiiiippiifiiiip",
     "nb_attention_pooled": "pipppppipppiiiiiippifiiip",
+    "nb_conv_rope_append": "piipipippppipippippiiiiiiiiiip",
+    "nb_conv_act": "piippiipippippiiiip",
+    "nb_conv_state_update": "piiipippiip",
+    "nb_attention_capped": "pippppippiiiiiiippiffip",
+    "nb_selective_scan_supported": "i",
+    "nb_selective_scan": "ppiiipppppiipippiipiip",
+    "nb_linear_attention_supported": "ii",
+    "nb_linear_attention": "piiiiippippiiipip",
+    "nb_glu_rows": "piiiipiiip",
+    "nb_cast_cols": "ppiiiiip",
+    "nb_rmsnorm_gated": "pppiipiiifp",
+    "nb_rms_pair_add": "ppppffppfpiiip",
     "nb_delta_rule_supported": "i",
     "nb_delta_rule": "piiiiiipppfffppppppiiiiip",
     "nb_layernorm": "pppppiiifp",

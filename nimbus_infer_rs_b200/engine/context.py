@@ -1,7 +1,7 @@
 """What a part sees of the step it runs in."""
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Any
 
 from .batch import BatchLayout
@@ -22,3 +22,5 @@ class StepContext:
     writes_cache: bool = True
     # what a layer's mixer leaves for the feed-forward beside it: (fp32 rows, first column)
     shared_projection: Any = None
+    # buffers that a part keeps for the rest of the step (keyed by the part)
+    scratch: dict = field(default_factory=dict)

@@ -63,7 +63,14 @@ class Model:
         self.embedding = TokenEmbedding(spec.vocab_size, spec.width, spec.embedding_scale)
         self.position = build_part("position", spec.position)
         self.layers = [Layer(i, ls) for i, ls in enumerate(spec.layers)]
-        self.final_norm = build_part("norm", spec.final_norm)
+        final_norm = spec.final_norm
+        if spec.logit_scale != 1.0:
+            # logits = head(norm(x)) * c = head(c * norm(x)): the constant rides on the norm
+            final_norm = final_norm.with_args(gain=spec.logit_scale)
+        self.final_norm = build_part("norm", final_norm)
+        self.stream_input = build_part("stream", spec.stream_input) \
+            if spec.stream_input is not None else None
+        self.stream_input_before = frozenset(spec.stream_input_before)
         self.head = LMHead(spec.vocab_size, spec.width, spec.tie_head)
         self.run_order = spec.run_order()
         self.params: dict[str, torch.Tensor | None] = {}
@@ -75,6 +82,8 @@ class Model:
         for l in self.layers:
             for name, part in l.parts().items():
                 yield f"layers.{l.index}.{name}.", part
+        if self.stream_input is not None:
+            yield "stream_input.", self.stream_input
         yield "final_norm.", self.final_norm
         yield "head.", self.head
 
@@ -94,6 +103,8 @@ class Model:
     def graph_safe(self) -> bool:
         """True if every part of the model may run under CUDA-graph capture."""
         parts = [self.embedding, self.position, self.final_norm, self.head]
+        if self.stream_input is not None:
+            parts.append(self.stream_input)
         for l in self.layers:
             parts += [l.block, *l.parts().values()]
         return all(getattr(p, "graph_safe", False) for p in parts)
@@ -118,8 +129,15 @@ class Model:
     def forward_hidden(self, ctx) -> torch.Tensor:
         """The fp32 residual stream after the last scheduled layer, [rows, width]."""
         x = self.embedding.forward(ctx, self.position)
+        x0 = x
+        if self.stream_input_before and min(self.stream_input_before) > 0:
+            # the layers add into the stream in place: the embedding's output is kept apart
+            x = torch.empty_like(x0)
+            ctx.ops.cast_cols(x0, x, 0)
         for entry, li in enumerate(self.run_order):
             layer = self.layers[li]
+            if entry in self.stream_input_before:
+                x = self.stream_input.forward(ctx, x, x0)
             ctx.kv, ctx.state, ctx.writes_cache = self.storage_of(ctx.cache, entry)
             ctx.kv_extra = ctx.cache.layer_kv_extra(entry)
             layer.block.forward(ctx, x, layer)

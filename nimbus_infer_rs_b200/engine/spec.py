@@ -8,6 +8,9 @@ its own each time), and a layer with ``cache_from`` set reads the key/value cach
 other layer instead of keeping its own.  A layer may have no feed-forward (``ffn=None``), and
 an arrangement in which both sublayers read one norm has no second norm (``norm_ffn=None``).
 ``max_seq_len=None``: nothing in the model bounds a sequence; the cache's size does.
+``stream_input`` with ``stream_input_before``: a part of the ``stream`` family (one set of
+parameters) that transforms the stream right before each of the named schedule entries, from
+the stream and the embedding's output.  ``logit_scale`` multiplies the logits.
 """
 from __future__ import annotations
 
@@ -43,6 +46,9 @@ class ModelSpec:
     tie_head: bool = True
     schedule: tuple[int, ...] | None = None
     embedding_scale: float = 1.0      # multiplies the token embedding (not the tied head)
+    logit_scale: float = 1.0          # multiplies the logits
+    stream_input: PartSpec | None = None
+    stream_input_before: tuple[int, ...] = ()     # schedule entries (positions in the run order)
 
     def run_order(self) -> tuple[int, ...]:
         order = self.schedule if self.schedule is not None else tuple(range(len(self.layers)))
@@ -52,7 +58,12 @@ class ModelSpec:
         return tuple(order)
 
     def validate(self) -> None:
-        self.run_order()
+        n_entries = len(self.run_order())
+        if self.stream_input_before and self.stream_input is None:
+            raise ValueError("stream_input_before names entries, but there is no stream_input")
+        for e in self.stream_input_before:
+            if not 0 <= e < n_entries:
+                raise ValueError(f"stream_input_before names entry {e} of {n_entries}")
         for i, l in enumerate(self.layers):
             if l.cache_from is not None:
                 if not 0 <= l.cache_from < len(self.layers) or l.cache_from == i:

@@ -7,9 +7,14 @@ from .position import LearnedAbsolute, NoPosition
 from .embedding import LMHead, TokenEmbedding
 from .attention import CausalSelfAttention
 from .latent_attention import LatentAttention
-from .feed_forward import DenseMLP
+from .feed_forward import DenseMLP, GatedMLP
 from .routed_experts import RoutedExperts
 from .block import ParallelBlock, PreNormBlock, SandwichBlock
 from .pooled_attention import PooledWindowAttention
 from .delta_rule import DeltaRule
 from .token_side import GatedTokenInput
+from .capped_attention import CappedAttention
+from .selective_scan import SelectiveScan
+from .linear_attention import DecayedLinearAttention
+from .mixer_pair import NormedPair
+from .stream_input import EmbeddingRemix

@@ -21,6 +21,8 @@ family         interface
                are ``None`` in a layer without them)
 ``side``       ``forward(ctx, x, x_act)``: a per-token input that a layer adds to the stream
                after its sublayers (``x_act``: the stream's rows in the activation type)
+``stream``     ``forward(ctx, x, x0) -> x'``: acts on the stream right before a schedule entry
+               (``x0``: the embedding's output); the model lists which entries
 =============  ===========================================================================
 
 Every part lists its parameters with :meth:`Part.param_specs` (shape and role) and gets the
@@ -194,7 +196,7 @@ class Block(Part):
 
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Part]]] = {
-    "norm": {}, "position": {}, "mixer": {}, "ffn": {}, "block": {}, "side": {},
+    "norm": {}, "position": {}, "mixer": {}, "ffn": {}, "block": {}, "side": {}, "stream": {},
 }
 
 

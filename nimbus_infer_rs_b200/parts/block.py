@@ -9,7 +9,10 @@ from .base import Block, register_part
 @register_part("block", "pre_norm")
 class PreNormBlock(Block):
     """``x += mixer(norm_mixer(x)); x += ffn(norm_ffn(x))`` (src/model.rs:297-300 with
-    :345-357, :437-439, :448-460, :485-487).  ``x`` is the fp32 residual stream."""
+    :345-357, :437-439, :448-460, :485-487).  ``x`` is the fp32 residual stream.  The
+    feed-forward may be absent (then the layer is its first half).  A mixer that adds its result
+    in a row pass of its own (``takes_next_norm``) is given the feed-forward's norm and hands
+    back that norm's rows, computed in the same pass."""
     graph_safe = True
 
     def __init__(self):
@@ -19,9 +22,15 @@ class PreNormBlock(Block):
         mixer, ffn = layer.mixer, layer.ffn
         h = layer.norm_mixer.defer(ctx, x) if mixer.accepts_deferred_norm \
             else layer.norm_mixer.forward(ctx, x)
-        mixer.forward(ctx, h, x)
-        h = layer.norm_ffn.defer(ctx, x) if ffn.accepts_deferred_norm \
-            else layer.norm_ffn.forward(ctx, x)
+        if ffn is None:
+            mixer.forward(ctx, h, x)
+            return
+        if getattr(mixer, "takes_next_norm", False) and hasattr(layer.norm_ffn, "add_into"):
+            h = mixer.forward(ctx, h, x, then=layer.norm_ffn)
+        else:
+            mixer.forward(ctx, h, x)
+            h = layer.norm_ffn.defer(ctx, x) if ffn.accepts_deferred_norm \
+                else layer.norm_ffn.forward(ctx, x)
         ffn.forward(ctx, h, x)
 
 

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from ..csrc.ops import ACTIVATIONS, ROW_ACTIVATIONS
+from ..csrc.ops import ACTIVATIONS, GLU_ACTIVATIONS, ROW_ACTIVATIONS
 from .base import VECTOR, FeedForward, ParamSpec, register_part
 from .linear import Linear
 
@@ -47,6 +47,41 @@ class DenseMLP(FeedForward):
             ctx.ops.act_rows(z, 0, self.act_code, self.act, mid)
         else:
             mid = self.fc(ctx, h, act=self.act_code)
+        if accumulate:
+            self.proj(ctx, mid, residual=residual)
+        else:
+            self.proj(ctx, mid, out=residual)
+
+
+@register_part("ffn", "gated_mlp")
+class GatedMLP(FeedForward):
+    """``residual += Wdown (act(Wgate h) * (Wup h))`` without biases; ``activation`` is ``relu``,
+    ``silu``, ``gelu_tanh``, ``gelu_erf``, ``relu2`` or ``none``.
+
+    One product gives ``[Wgate h | Wup h]`` side by side in fp32; a row pass applies the
+    activation to the first half, multiplies by the second (both unrounded) and hands the
+    product to ``Wdown`` in the activation type."""
+    graph_safe = True
+    can_overwrite = True
+
+    def __init__(self, width: int, hidden: int, activation: str):
+        if activation not in GLU_ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r} (have {sorted(GLU_ACTIVATIONS)})")
+        self.width, self.hidden = int(width), int(hidden)
+        self.activation = activation
+        self.act_code = GLU_ACTIVATIONS[activation]
+        # the two halves start on multiples of 8 columns (fp32 rows on 32-byte boundaries)
+        self.half = -(-self.hidden // 8) * 8
+        self.fc = Linear(self.width, 2 * self.half, bias=False)
+        self.proj = Linear(self.hidden, self.width, bias=False)
+
+    def children(self):
+        return {"fc": self.fc, "proj": self.proj}
+
+    def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
+        both = self.fc(ctx, h, out_dtype=torch.float32)
+        mid = torch.empty((both.shape[0], self.hidden), device=both.device, dtype=ctx.rt.act_dtype)
+        ctx.ops.glu_rows(both, 0, self.half, self.act_code, mid)
         if accumulate:
             self.proj(ctx, mid, residual=residual)
         else:

@@ -39,13 +39,21 @@ class RMSNorm(Norm):
     defers: one launch gives the rows to every reader."""
     graph_safe = True
 
-    def __init__(self, width: int, eps: float):
+    def __init__(self, width: int, eps: float, gain: float = 1.0):
+        """``gain``: a constant that multiplies the result (a model that scales its logits does
+        so through its last norm); folded into the weight when it is bound."""
         self.width = int(width)
         self.eps = float(eps)
+        self.gain = float(gain)
         self.weight = None
 
     def param_specs(self):
         return {"weight": ParamSpec((self.width,), VECTOR)}
+
+    def bind(self, params, runtime) -> None:
+        super().bind(params, runtime)
+        if self.gain != 1.0 and self.weight is not None:
+            self.weight = (self.weight * self.gain).contiguous()
 
     def forward(self, ctx, x, rows=None, n_rows=None):
         n = x.shape[0] if rows is None else (rows.numel() if n_rows is None else n_rows)

@@ -43,3 +43,29 @@ def rotary_frequencies(dims: int, base: float, scaling: dict | None = None):
         f = f / factor * ramp + f * (1.0 - ramp)
         amplitude = 0.1 * math.log(factor) + 1.0
     return f.to(torch.float32), float(amplitude)
+
+
+def rotary_frequencies_by_wavelength(dims: int, base: float, scaling: dict | None = None):
+    """fp32 tensor ``[dims/2]`` of ``f_i = base^(-2i/dims)``, with scaling by wavelength for
+    contexts longer than the ``original`` one (``factor, low, high, original``): a pair whose
+    wavelength ``2 pi / f`` is shorter than ``original / high`` keeps its frequency, one longer
+    than ``original / low`` gets ``f / factor``, and between the two, with ``s = (original /
+    wavelength - low) / (high - low)``, the blend ``(1 - s) f / factor + s f``.  cos and sin
+    keep their size."""
+    dims = int(dims)
+    if dims < 2 or dims % 2:
+        raise ValueError(f"rotated dimensions come in pairs, got dims={dims}")
+    out = []
+    for i in range(dims // 2):
+        f = float(base) ** (-2.0 * i / dims)
+        if scaling:
+            factor, original = float(scaling["factor"]), float(scaling["original"])
+            low, high = float(scaling["low"]), float(scaling["high"])
+            wavelength = 2.0 * math.pi / f
+            if wavelength > original / low:
+                f = f / factor
+            elif wavelength >= original / high:
+                s = (original / wavelength - low) / (high - low)
+                f = (1.0 - s) * f / factor + s * f
+        out.append(f)
+    return torch.tensor(out, dtype=torch.float64).to(torch.float32)

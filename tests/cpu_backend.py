@@ -70,7 +70,7 @@ class CpuBackend:
             neg = torch.clamp(z, max=0.0)
             y = torch.where(z > 0, ap * z * z + 0.5 * z, an * (torch.expm1(neg) - neg) + 0.5 * z)
         else:
-            raise ValueError(act)
+            y = self._act(z, act)       # what a product's epilogue can apply, or nothing
         out.copy_(y.to(out.dtype))
 
     def gather_mul(self, g, table, tokens, out):
@@ -173,6 +173,157 @@ class CpuBackend:
             o = torch.einsum("hkv,hk->hv", S, rr)
             o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps)
             out[r] = (o.reshape(hd) * norm_w * g).to(out.dtype)
+
+    # -- short convolutions, capped attention, linear recurrences (row by row, in order) ---
+    @staticmethod
+    def _act(x, act):
+        if act == 3:
+            return x * torch.sigmoid(x)
+        if act == 7:
+            return torch.relu(x)
+        if act == 4:
+            return torch.relu(x) ** 2
+        if act == 1:
+            return 0.5 * x * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * x ** 3)))
+        if act == 2:
+            return 0.5 * x * (1.0 + torch.erf(x / math.sqrt(2.0)))
+        assert act == 0
+        return x
+
+    @staticmethod
+    def _conv_row(u, w, taps, state_row, C):
+        """One token through the convolution: its result, and the state moved on by one."""
+        if taps <= 0:
+            return u
+        past = state_row.view(taps - 1, C) if taps > 1 else u.new_zeros((0, C))
+        window = torch.cat([past, u[None]])                      # [taps, C], oldest first
+        y = (window * w.t()).sum(0)
+        if taps > 1:
+            state_row.copy_(window[1:].reshape(-1))
+        return y
+
+    def conv_rope_append(self, src, col0, w, taps, state, freq, rot_dims, layout, k_store,
+                         v_store, n_heads, dv, q_out):
+        d, G = k_store.head_dim, k_store.n_kv_heads
+        qw, kw = n_heads * d, G * d
+        C = qw + kw + G * dv
+        taps = int(taps) if w is not None else 0
+
+        def turn(x, pos):
+            if not rot_dims:
+                return x
+            ang = (torch.tensor(float(pos), dtype=torch.float32) * freq).float()
+            c, s = torch.cos(ang), torch.sin(ang)
+            u, v = x[:, 0:rot_dims:2], x[:, 1:rot_dims:2]
+            out = x.clone()
+            out[:, 0:rot_dims:2] = u * c - v * s
+            out[:, 1:rot_dims:2] = v * c + u * s
+            return out
+
+        for r in range(layout.n_rows):
+            slot = int(layout.row_slot[r])
+            if slot < 0:
+                q_out[r].zero_()
+                continue
+            pos = int(layout.row_pos[r])
+            y = self._conv_row(src[r, col0:col0 + C].float(), w, taps,
+                               state[slot] if taps > 1 else None, C)
+            q_out[r] = turn(y[:qw].view(n_heads, d), pos).reshape(-1).to(q_out.dtype)
+            self._entry(k_store, k_store.k, slot, pos)[:] = turn(y[qw:qw + kw].view(G, d), pos).to(k_store.k.dtype)
+            self._entry(v_store, v_store.k, slot, pos)[:] = y[qw + kw:].view(G, dv).to(v_store.k.dtype)
+
+    def conv_act(self, src, col0, w, bias, taps, act, state, layout, out_f32, out_act=None):
+        C = out_f32.shape[1]
+        taps = int(taps) if w is not None else 0
+        for r in range(layout.n_rows):
+            slot = int(layout.row_slot[r])
+            if slot < 0:
+                out_f32[r].zero_()
+                continue
+            y = self._conv_row(src[r, col0:col0 + C].float(), w, taps,
+                               state[slot] if taps > 1 else None, C)
+            if bias is not None:
+                y = y + bias
+            out_f32[r] = self._act(y, act)
+        if out_act is not None and out_act is not out_f32:
+            out_act.copy_(out_f32.to(out_act.dtype))
+
+    def attention_capped(self, q, layout, k_store, v_store, n_heads, sink, out, scale, softcap):
+        d, dv, G = k_store.head_dim, v_store.head_dim, k_store.n_kv_heads
+        group = n_heads // G
+        for r in range(layout.n_rows):
+            slot = int(layout.row_slot[r])
+            if slot < 0:
+                out[r].zero_()
+                continue
+            pos = int(layout.row_pos[r])
+            keys = torch.stack([self._entry(k_store, k_store.k, slot, j).float() for j in range(pos + 1)])
+            vals = torch.stack([self._entry(v_store, v_store.k, slot, j).float() for j in range(pos + 1)])
+            qr = q[r].float().view(n_heads, d)
+            for h in range(n_heads):
+                s = (keys[:, h // group] @ qr[h]) * scale
+                if softcap:
+                    s = softcap * torch.tanh(s / softcap)
+                m = s.max() if sink is None else torch.maximum(s.max(), sink[h])
+                e = torch.exp(s - m)
+                den = e.sum() + (torch.exp(sink[h] - m) if sink is not None else 0.0)
+                out[r, h * dv:(h + 1) * dv] = ((e / den) @ vals[:, h // group]).to(out.dtype)
+
+    def selective_scan(self, x, low, col_b, col_c, dt_lin, dt_bias, a_log, d_skip, z, z_col, state,
+                       layout, n_state, out):
+        inner, N = x.shape[1], n_state
+        A = -torch.exp(a_log.float())
+        for r in range(layout.n_rows):
+            slot = int(layout.row_slot[r])
+            if slot < 0:
+                out[r].zero_()
+                continue
+            dt = torch.nn.functional.softplus(dt_lin[r].float() + dt_bias)
+            xr, B, C = x[r].float(), low[r, col_b:col_b + N].float(), low[r, col_c:col_c + N].float()
+            S = state[slot].view(inner, N)
+            S.copy_(torch.exp(dt[:, None] * A) * S + (dt * xr)[:, None] * B[None, :])
+            y = S @ C + d_skip * xr
+            zr = z[r, z_col:z_col + inner].float()
+            out[r] = (y * zr * torch.sigmoid(zr)).to(out.dtype)
+
+    def linear_attention(self, fused, col_q, col_k, col_v, act, decay, state, layout, n_heads, d, dv,
+                         out):
+        H = n_heads
+        for r in range(layout.n_rows):
+            slot = int(layout.row_slot[r])
+            if slot < 0:
+                out[r].zero_()
+                continue
+            row = fused[r].float()
+            q = self._act(row[col_q:col_q + H * d], act).view(H, d)
+            k = self._act(row[col_k:col_k + H * d], act).view(H, d)
+            v = self._act(row[col_v:col_v + H * dv], act).view(H, dv)
+            S = state[slot].view(H, d, dv)
+            S.copy_(decay[:, None, None] * S + k[:, :, None] * v[:, None, :])
+            out[r] = torch.einsum("hkv,hk->hv", S, q).reshape(-1)
+
+    def rmsnorm_gated(self, x, gamma, gate, gate_col, eps, out):
+        n, d = out.shape
+        xr = x[:n].float()
+        y = xr / torch.sqrt((xr * xr).mean(-1, keepdim=True) + eps) * gamma
+        out.copy_((y * torch.sigmoid(gate[:n, gate_col:gate_col + d].float())).to(out.dtype))
+
+    def rms_pair_add(self, a, gamma_a, b, gamma_b, eps, coef, residual, next_gamma=None,
+                     next_eps=0.0, out_next=None):
+        def unit(t):
+            return t / torch.sqrt((t * t).mean(-1, keepdim=True) + eps)
+        residual += coef * (unit(a.float()) * gamma_a + unit(b.float()) * gamma_b)
+        if out_next is not None:
+            u = residual / torch.sqrt((residual * residual).mean(-1, keepdim=True) + next_eps)
+            out_next.copy_((u * next_gamma).to(out_next.dtype))
+
+    def glu_rows(self, x, gate_col, up_col, act, out):
+        n, d = out.shape
+        out.copy_((self._act(x[:n, gate_col:gate_col + d].float(), act)
+                   * x[:n, up_col:up_col + d].float()).to(out.dtype))
+
+    def cast_cols(self, x, out, out_col):
+        out[:, out_col:out_col + x.shape[1]] = x.to(out.dtype)
 
     def latent_append(self, src, col, gamma, eps, layout, kv):
         rank = kv.head_dim
