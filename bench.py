@@ -290,7 +290,9 @@ def run_workload(engine, cfg, prompt_lens, n_new, hbm_gbs, windows=()):
 # --designs: Runesun beside GPT-2 at equal layer sizes
 # ---------------------------------------------------------------------------------------------
 DESIGN_PAIRS = {"runesun": (("runesun-2k", "gpt2-2k"), ("runesun-1k", "gpt2-1k")),
-                "rizitar": (("rizitar-2k", "gpt2-2k"), ("rizitar-1k", "gpt2-1k"))}
+                "rizitar": (("rizitar-2k", "gpt2-2k"), ("rizitar-1k", "gpt2-1k")),
+                # beside the closest design of the library: recurrent layers among attention layers
+                "pinozen": (("pinozen-2k", "rizitar-2k"), ("pinozen-1k", "rizitar-1k"))}
 
 
 class OpTimer:
@@ -301,7 +303,9 @@ class OpTimer:
     KINDS = ("linear", "layernorm", "rmsnorm", "attention", "attention_latent", "latent_append",
              "head_linear", "moe_route", "moe_group", "moe_linear", "moe_combine", "embed_pos",
              "rms_add", "act_rows", "gather_mul", "qk_norm_rope_append", "pool_blocks",
-             "attention_pooled", "delta_rule")
+             "attention_pooled", "delta_rule", "conv_rope_append", "conv_act", "attention_capped",
+             "selective_scan", "linear_attention", "rmsnorm_gated", "rms_pair_add", "glu_rows",
+             "cast_cols")
 
     def __init__(self, ops):
         import torch
@@ -401,6 +405,41 @@ class OpTimer:
             # every sequence's window and blocks once (a row's neighbours share them), queries, outputs
             keys = sum(seen(p + n - 1) + (n - 1 if window else 0) for p, n in zip(lay.seq_pos0_host, lay.seq_lens))
             return keys * per_key * 2 * elt + 2 * lay.n_tokens * width * elt, 4 * pairs * width
+        if kind == "conv_rope_append":
+            w, taps, lay, ks, vs, heads, q = a[2], a[3], a[7], a[8], a[9], a[10], a[12]
+            ch = heads * ks.head_dim + ks.n_kv_heads * (ks.head_dim + vs.head_dim)
+            # the projected rows once, the cached keys and values, the queries, the state in and out
+            return lay.n_tokens * (4 * ch + (ch - heads * ks.head_dim) * ks.k.element_size()) + nb(q, w) + \
+                2 * lay.n_seqs * max(int(taps) - 1, 0) * ch * 4, 0
+        if kind == "conv_act":
+            w, taps, lay, out, out_act = a[2], a[4], a[7], a[8], (a[9] if len(a) > 9 else None)
+            return 4 * out.numel() + nb(out, out_act, w) + 2 * lay.n_seqs * max(int(taps) - 1, 0) * out.shape[1] * 4, 0
+        if kind == "attention_capped":
+            q, lay, ks, vs, heads, out = a[0], a[1], a[2], a[3], a[4], a[6]
+            elt = ks.k.element_size()
+            keys = sum(p + n for p, n in zip(lay.seq_pos0_host, lay.seq_lens))
+            pairs = sum(n * p + n * (n + 1) // 2 for p, n in zip(lay.seq_pos0_host, lay.seq_lens))
+            return keys * ks.n_kv_heads * (ks.head_dim + vs.head_dim) * elt + nb(q, out), \
+                2 * pairs * heads * (ks.head_dim + vs.head_dim)
+        if kind == "selective_scan":
+            x, low, dt_lin, lay, n_state, out = a[0], a[1], a[4], a[11], a[12], a[13]
+            inner = x.shape[1]
+            # inputs, step sizes and gates per token, B and C, the state of every sequence in and
+            # out; per token, channel and state number an exponential and three multiply-adds
+            return lay.n_tokens * (3 * inner + 2 * n_state) * 4 + nb(out) + 2 * lay.n_seqs * inner * n_state * 4, \
+                2 * 4 * lay.n_tokens * inner * n_state
+        if kind == "linear_attention":
+            lay, heads, d, dv, out = a[7], a[8], a[9], a[10], a[11]
+            return lay.n_tokens * heads * (2 * d + dv) * 4 + nb(out) + 2 * lay.n_seqs * heads * d * dv * 4, \
+                2 * 2 * lay.n_tokens * heads * d * dv
+        if kind == "rmsnorm_gated":
+            return 2 * 4 * a[5].numel() + nb(a[5]), 0
+        if kind == "rms_pair_add":
+            return nb(a[0], a[2], kw.get("out_next", a[9] if len(a) > 9 else None)) + 2 * nb(a[6]), 0
+        if kind == "glu_rows":
+            return 2 * 4 * a[4].numel() + nb(a[4]), 0
+        if kind == "cast_cols":
+            return nb(a[0]) + a[0].numel() * a[1].element_size(), 0
         if kind == "delta_rule":
             fused, lay, state, heads, dim, out = a[0], a[12], a[13], a[14], a[15], a[16]
             hd = heads * dim

@@ -23,6 +23,24 @@ __device__ __forceinline__ float nb_exp2(float x) {
   return y;
 }
 
+// softcap * tanh(raw * cap_in), with tanh(t) = 1 - 2 / (1 + e^(2t)) on the hardware's exponential
+// and reciprocal: the absolute error is about 2e-7 * softcap for every t (the ends give -1 and 1).
+__device__ __forceinline__ float nb_softcap(float raw, float cap_in, float softcap) {
+  const float e = nb_exp2(raw * cap_in * 2.8853900817779268f);
+  return softcap * (1.0f - __fdividef(2.0f, 1.0f + e));
+}
+
+// The softmax's last step when its denominator has one more term exp(sink) without key or
+// value: sum `l` and weighted values `a` are in units of exp(m) (base 2 when `base2`); returns
+// the factor for `a` after adding the term to `l`.
+__device__ __forceinline__ float nb_sink_fix(float& l, float m, float sink_logit, bool base2) {
+  const float sk = base2 ? sink_logit * 1.4426950408889634f : sink_logit;
+  const float m_f = fmaxf(m, sk);
+  const float fix = (m == -INFINITY) ? 0.0f : (base2 ? nb_exp2(m - m_f) : expf(m - m_f));
+  l = fmaf(l, fix, base2 ? nb_exp2(sk - m_f) : expf(sk - m_f));
+  return fix;
+}
+
 template <typename T>
 struct Lane16;   // the 16 bytes a lane reads, as floats
 template <>

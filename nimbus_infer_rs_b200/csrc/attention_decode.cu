@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(THREADS)
 attention_decode_kernel(const T* q, int q_stride, int q_col,
                         const int* row_slot, const int* row_pos,
                         NbPagedKV kv, int group, TOut* out, int out_stride,
-                        float scale, int window, int n_splits, float* part_acc,
+                        float scale, float softcap, const float* sink, int window, int n_splits, float* part_acc,
                         float* part_ml, int* counters, int append,
                         int k_col, int v_col) {
   constexpr int EPL = Lane16<T>::N;           // elements per lane
@@ -128,7 +128,7 @@ attention_decode_kernel(const T* q, int q_stride, int q_col,
     __syncthreads();
     T* kt = tiles + (size_t)stage * 2 * TILE;
     T* vt = kt + TILE;
-    if (append && p == pos / PAGE_TOKENS) {
+    if (append > 0 && p == pos / PAGE_TOKENS) {
       // this step's own key and value (row r of the projection output) belong at token `pos`
       // of this page: put them into the staged tile and into the cache
       const int in_page = pos % PAGE_TOKENS;
@@ -164,7 +164,9 @@ attention_decode_kernel(const T* q, int q_stride, int q_col,
         for (int e = 0; e < EPL; ++e) dot = fmaf(qreg[gh][e], kf[e], dot);
 #pragma unroll
         for (int o = LPR / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        const float s = valid ? dot * scale : -INFINITY;
+        float s = dot * scale;
+        if (softcap > 0.0f) s = softcap * tanhf(s / softcap);
+        if (!valid) s = -INFINITY;
         float mx = s;
 #pragma unroll
         for (int o = LPR; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -219,6 +221,7 @@ attention_decode_kernel(const T* q, int q_stride, int q_col,
     }
     const int head = kvh * group + gh;
     if (n_splits == 1) {   // nothing to merge with: this is the result
+      if (sink != nullptr) a *= nb_sink_fix(l, M, sink[head], false);
       out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
       continue;
     }
@@ -254,6 +257,7 @@ attention_decode_kernel(const T* q, int q_stride, int q_col,
       a += f * __ldcg(&part_acc[(base + s) * HD + c]);
       l += f * __ldcg(&part_ml[(base + s) * 2 + 1]);
     }
+    if (sink != nullptr) a *= nb_sink_fix(l, M, sink[head], false);
     out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
   }
 }
@@ -304,7 +308,7 @@ __global__ void __launch_bounds__(NW * 32)
 attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
                             const int* row_slot, const int* row_pos,
                             NbPagedKV kv, int group, TOut* out, int out_stride,
-                            float scale, int window, int n_splits, float* part_acc,
+                            float scale, float softcap, const float* sink, int window, int n_splits, float* part_acc,
                             float* part_ml, int* counters, int append,
                             int k_col, int v_col) {
   typedef __nv_bfloat16 bf16;
@@ -376,6 +380,9 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
       cp_async16(vdst + row * ROW + c * 8, vsrc + row * HD + c * 8);
     }
   };
+  // append < 0: the kernel in front of this one wrote the step's key and value into the cache
+  // itself; no page may be asked for before it is done.
+  if (append < 0) nb_grid_dependency_wait();
   // one commit group per stage of the ring, also an empty one: the count of groups in flight
   // then says which page has landed
 #pragma unroll
@@ -410,7 +417,8 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-  const float sl2 = scale * 1.4426950408889634f;
+  const float sl2 = (softcap > 0.0f ? 1.0f : scale) * 1.4426950408889634f;
+  const float cap_in = softcap > 0.0f ? scale / softcap : 0.0f;
 
   int stage = 0;
   for (int p0 = p_begin; p0 < p_end; p0 += PPI) {
@@ -422,7 +430,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
     if (p >= p_end) break;
     bf16* kt = tiles + (size_t)(stage + q2) * 2 * STILE;
     bf16* vt = kt + STILE;
-    const bool own_page = append && p == pos / PAGE_TOKENS;
+    const bool own_page = append > 0 && p == pos / PAGE_TOKENS;
     const int tail_row = kv_len - p * PAGE_TOKENS;   // first row of the page that holds no key yet
     if (own_page || tail_row < PAGE_TOKENS) {        // uniform over the CTA
       constexpr int CPR = HD / 8;
@@ -481,6 +489,10 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
       }
       const int ja = key0 + g, jb = ja + 8;
       const bool va = ja >= j_begin && ja < kv_len, vb = jb >= j_begin && jb < kv_len;
+      if (softcap > 0.0f) {   // uniform: capped scores carry their scale already
+#pragma unroll
+        for (int j = 0; j < 4; ++j) sc[j] = nb_softcap(sc[j], cap_in, softcap);
+      }
       const float s0 = va ? sc[0] * sl2 : -INFINITY, s1 = va ? sc[1] * sl2 : -INFINITY;
       const float s2 = vb ? sc[2] * sl2 : -INFINITY, s3 = vb ? sc[3] * sl2 : -INFINITY;
       float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
@@ -575,6 +587,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
     }
     const int head = kvh * group + gh;
     if (n_splits == 1) {
+      if (sink != nullptr) a *= nb_sink_fix(l, M, sink[head], true);
       out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
       continue;
     }
@@ -614,6 +627,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
         a += f * row[s * step + c];
         l += f * row[s * step + HD + 1];
       }
+      if (sink != nullptr) a *= nb_sink_fix(l, M, sink[kvh * group + gh], true);
       out[(size_t)r * out_stride + (size_t)(kvh * group + gh) * HD + c] =
           nb_from_f32<TOut>(l > 0.0f ? a / l : a);
     }
@@ -660,13 +674,14 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
       }
       M = Mn;
     }
+    if (sink != nullptr) a *= nb_sink_fix(l, M, sink[head], true);
     out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
   }
 }
 
 template <int HD, typename TOut, int MMA_STAGES, int NW>
 int launch_mma_s(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
-                 const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
+                 const NbPagedKV& kv, int group, void* out, int out_stride, float scale, float softcap, const float* sink, int window,
                  int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
                  int k_col, int v_col, bool clustered, cudaStream_t stream) {
   const size_t tiles = (size_t)2 * MMA_STAGES * PAGE_TOKENS * (HD + 8) * sizeof(__nv_bfloat16);
@@ -683,7 +698,7 @@ int launch_mma_s(const void* q, int q_stride, int q_col, const int* row_slot, co
     const size_t smem = tiles + (size_t)n_splits * group * (HD + 2) * sizeof(float);
     NB_CUDA(nb_launch_clusters(kern, grid, dim3(NW * 32), smem, stream, n_splits,
                                (const __nv_bfloat16*)q, q_stride, q_col, row_slot, row_pos, kv, group,
-                               (TOut*)out, out_stride, scale, window, n_splits, part_acc, part_ml,
+                               (TOut*)out, out_stride, scale, softcap, sink, window, n_splits, part_acc, part_ml,
                                counters, append, k_col, v_col));
     return 0;
   }
@@ -694,14 +709,14 @@ int launch_mma_s(const void* q, int q_stride, int q_col, const int* row_slot, co
     configured = true;
   }
   NB_CUDA(nb_launch(kern, grid, dim3(NW * 32), tiles, stream, (const __nv_bfloat16*)q, q_stride, q_col,
-                    row_slot, row_pos, kv, group, (TOut*)out, out_stride, scale, window, n_splits,
+                    row_slot, row_pos, kv, group, (TOut*)out, out_stride, scale, softcap, sink, window, n_splits,
                     part_acc, part_ml, counters, append, k_col, v_col));
   return 0;
 }
 
 template <int HD, typename TOut>
 int launch_mma(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
-               const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
+               const NbPagedKV& kv, int group, void* out, int out_stride, float scale, float softcap, const float* sink, int window,
                int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
                int k_col, int v_col, bool clustered, cudaStream_t stream) {
   static int sms = 0;
@@ -721,20 +736,20 @@ int launch_mma(const void* q, int q_stride, int q_col, const int* row_slot, cons
   if (per_sm > 8) per_sm = 8;   // 2,048 threads an SM
   if (ctas <= per_sm * sms)
     return launch_mma_s<HD, TOut, 4, 8>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride,
-                                        scale, window, n_rows, n_splits, part_acc, part_ml, counters,
+                                        scale, softcap, sink, window, n_rows, n_splits, part_acc, part_ml, counters,
                                         append, k_col, v_col, clustered, stream);
   return launch_mma_s<HD, TOut, 2, 4>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride,
-                                      scale, window, n_rows, n_splits, part_acc, part_ml, counters, append,
+                                      scale, softcap, sink, window, n_rows, n_splits, part_acc, part_ml, counters, append,
                                       k_col, v_col, clustered, stream);
 }
 
 template <typename TOut>
 int mma_by_head_dim(int hd, const void* q, int q_stride, int q_col, const int* row_slot,
                     const int* row_pos, const NbPagedKV& kv, int group, void* out, int out_stride,
-                    float scale, int window, int n_rows, int n_splits, float* pa, float* pm,
+                    float scale, float softcap, const float* sink, int window, int n_rows, int n_splits, float* pa, float* pm,
                     int* cn, int ap, int kc, int vc, bool clustered, cudaStream_t st) {
 #define NB_HD(HD_) \
-  case HD_: return launch_mma<HD_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, pa, pm, cn, ap, kc, vc, clustered, st)
+  case HD_: return launch_mma<HD_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, softcap, sink, window, n_rows, n_splits, pa, pm, cn, ap, kc, vc, clustered, st)
   switch (hd) {
     NB_HD(16); NB_HD(32); NB_HD(48); NB_HD(64); NB_HD(80); NB_HD(96); NB_HD(112); NB_HD(128);
   }
@@ -744,7 +759,7 @@ int mma_by_head_dim(int hd, const void* q, int q_stride, int q_col, const int* r
 
 template <typename T, int HD, int G, typename TOut>
 int launch(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
-           const NbPagedKV& kv, int group, void* out, int out_stride, float scale, int window,
+           const NbPagedKV& kv, int group, void* out, int out_stride, float scale, float softcap, const float* sink, int window,
            int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
            int k_col, int v_col, cudaStream_t stream) {
   const size_t smem = (size_t)4 * PAGE_TOKENS * HD * sizeof(T) +
@@ -754,18 +769,18 @@ int launch(const void* q, int q_stride, int q_col, const int* row_slot, const in
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(n_splits, kv.n_kv_heads, n_rows);
   NB_CUDA(nb_launch(kern, grid, dim3(THREADS), smem, stream, (const T*)q, q_stride, q_col, row_slot,
-                    row_pos, kv, group, (TOut*)out, out_stride, scale, window, n_splits, part_acc,
+                    row_pos, kv, group, (TOut*)out, out_stride, scale, softcap, sink, window, n_splits, part_acc,
                     part_ml, counters, append, k_col, v_col));
   return 0;
 }
 
 template <typename T, int HD, typename TOut>
 int by_group(int group, const void* q, int q_stride, int q_col, const int* row_slot,
-             const int* row_pos, const NbPagedKV& kv, void* out, int out_stride, float scale,
-             int window, int n_rows, int n_splits, float* pa, float* pm, int* cn, int ap,
+             const int* row_pos, const NbPagedKV& kv, void* out, int out_stride, float scale, float softcap,
+             const float* sink, int window, int n_rows, int n_splits, float* pa, float* pm, int* cn, int ap,
              int kc, int vc, cudaStream_t st) {
 #define NB_G(G_) \
-  return launch<T, HD, G_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, pa, pm, cn, ap, kc, vc, st)
+  return launch<T, HD, G_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, softcap, sink, window, n_rows, n_splits, pa, pm, cn, ap, kc, vc, st)
   if (group == 1) NB_G(1);
   if (group == 2) NB_G(2);
   if (group <= 4) NB_G(4);
@@ -775,11 +790,11 @@ int by_group(int group, const void* q, int q_stride, int q_col, const int* row_s
 
 template <typename T, typename TOut>
 int by_head_dim(int hd, int group, const void* q, int q_stride, int q_col, const int* row_slot,
-                const int* row_pos, const NbPagedKV& kv, void* out, int out_stride, float scale,
-                int window, int n_rows, int n_splits, float* pa, float* pm, int* cn, int ap,
+                const int* row_pos, const NbPagedKV& kv, void* out, int out_stride, float scale, float softcap,
+                const float* sink, int window, int n_rows, int n_splits, float* pa, float* pm, int* cn, int ap,
                 int kc, int vc, cudaStream_t st) {
 #define NB_HD(HD_) \
-  return by_group<T, HD_, TOut>(group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, window, n_rows, n_splits, pa, pm, cn, ap, kc, vc, st)
+  return by_group<T, HD_, TOut>(group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, softcap, sink, window, n_rows, n_splits, pa, pm, cn, ap, kc, vc, st)
   switch (hd) {
     case 16: NB_HD(16);
     case 32: NB_HD(32);
@@ -820,7 +835,7 @@ std::atomic<int> g_cluster_merge{1};
 int attention_decode(const void* q, int dtype, int q_stride, int q_col, const int* row_slot,
                      const int* row_pos, const void* k_cache, const void* v_cache,
                      const int* block_table, int max_pages, int page, int n_heads, int n_kv_heads,
-                     int head_dim, void* out, int out_dtype, int out_stride, float scale, int window,
+                     int head_dim, void* out, int out_dtype, int out_stride, float scale, float softcap, const float* sink, int window,
                      int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters,
                      int append, int k_col, int v_col, int clusters_allowed, cudaStream_t stream) {
   if (n_rows == 0) return 0;
@@ -831,7 +846,7 @@ int attention_decode(const void* q, int dtype, int q_stride, int q_col, const in
   NB_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_rows <= 65535 && n_kv_heads <= 65535,
              NB_ERR_UNSUPPORTED, "attention_decode: grid too large");
   NB_REQUIRE(part_acc && part_ml && counters, NB_ERR_BAD_ARG, "attention_decode: scratch missing");
-  if (append) {
+  if (append > 0) {
     const int epl = dtype == NB_F32 ? 4 : 8;
     NB_REQUIRE(q_stride % epl == 0 && k_col % epl == 0 && v_col % epl == 0 && (uintptr_t)q % 16 == 0,
                NB_ERR_UNSUPPORTED, "attention_decode: keys/values to append must be 16-byte aligned");
@@ -840,7 +855,7 @@ int attention_decode(const void* q, int dtype, int q_stride, int q_col, const in
   const int group = n_heads / n_kv_heads;
   typedef __nv_bfloat16 bf16;
   int rc;
-#define NB_ARGS head_dim, group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, stream
+#define NB_ARGS head_dim, group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, softcap, sink, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, stream
   if (dtype == NB_F32) {
     rc = out_dtype == NB_F32 ? by_head_dim<float, float>(NB_ARGS) : by_head_dim<float, bf16>(NB_ARGS);
   } else {
@@ -851,8 +866,8 @@ int attention_decode(const void* q, int dtype, int q_stride, int q_col, const in
     // through the scratch arrays and a counter
     const bool clustered = clusters_allowed > 0 && n_splits >= 2 && n_splits <= MAX_CLUSTER;
     rc = out_dtype == NB_F32
-             ? mma_by_head_dim<float>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, clustered, stream)
-             : mma_by_head_dim<bf16>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, clustered, stream);
+             ? mma_by_head_dim<float>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, softcap, sink, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, clustered, stream)
+             : mma_by_head_dim<bf16>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, softcap, sink, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, clustered, stream);
   }
 #undef NB_ARGS
   if (rc) return rc;
@@ -871,8 +886,28 @@ NB_EXPORT int nb_attention_decode(const void* q, int dtype, int q_stride, int q_
                                   cudaStream_t stream) {
   return attention_decode(q, dtype, q_stride, q_col, row_slot, row_pos, k_cache, v_cache, block_table,
                           max_pages, page, n_heads, n_kv_heads, head_dim, out, out_dtype, out_stride,
-                          scale, window, n_rows, n_splits, part_acc, part_ml, counters, append, k_col,
-                          v_col, g_cluster_merge.load(), stream);
+                          scale, 0.0f, nullptr, window, n_rows, n_splits, part_acc, part_ml, counters,
+                          append, k_col, v_col, g_cluster_merge.load(), stream);
+}
+
+// The same with capped scores (softcap > 0: a score becomes softcap * tanh(score / softcap)) and
+// a sink (fp32 [n_heads] logits of one more term of the softmax's denominator, without key or
+// value; null for none).  The step's keys and values are in the cache already, written by the
+// kernel launched before this one: the pages are asked for only after that kernel is done.
+NB_EXPORT int nb_attention_decode_capped(const void* q, int dtype, int q_stride, int q_col,
+                                         const int* row_slot, const int* row_pos,
+                                         const void* k_cache, const void* v_cache,
+                                         const int* block_table, int max_pages, int page,
+                                         int n_heads, int n_kv_heads, int head_dim, void* out,
+                                         int out_dtype, int out_stride, float scale, float softcap,
+                                         const float* sink, int window, int n_rows, int n_splits,
+                                         float* part_acc, float* part_ml, int* counters,
+                                         cudaStream_t stream) {
+  NB_REQUIRE(softcap >= 0.0f, NB_ERR_BAD_ARG, "attention_decode: a cap is positive, or 0 for none");
+  return attention_decode(q, dtype, q_stride, q_col, row_slot, row_pos, k_cache, v_cache, block_table,
+                          max_pages, page, n_heads, n_kv_heads, head_dim, out, out_dtype, out_stride,
+                          scale, softcap, sink, window, n_rows, n_splits, part_acc, part_ml, counters,
+                          /*append=*/-1, 0, 0, g_cluster_merge.load(), stream);
 }
 
 // How the splits of the bfloat16 kernel merge: 0 always through the scratch arrays; otherwise
@@ -960,7 +995,7 @@ NB_EXPORT int nb_attention_decode_static(const void* q, int dtype, int q_stride,
   // always through the scratch arrays: this entry point exists for them
   return attention_decode(q, dtype, q_stride, q_col, row_slot, row_pos, k_cache, v_cache,
                           block_table, max_pages, page, n_heads, n_kv_heads, head_dim, out,
-                          out_dtype, out_stride, scale, window, n_rows, n_splits,
+                          out_dtype, out_stride, scale, 0.0f, nullptr, window, n_rows, n_splits,
                           reinterpret_cast<float*>(base + cnt_b + ml_b),
                           reinterpret_cast<float*>(base + cnt_b),
                           reinterpret_cast<int*>(base), /*append=*/0, 0, 0,

@@ -93,7 +93,7 @@ struct AttnSmem {
   static constexpr int TMEM_COLS = 512;
 };
 
-template <int HD, typename TOut>
+template <int HD, typename TOut, bool CAP>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const __grid_constant__ CUtensorMap map_k,
@@ -103,7 +103,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const int* cu_rows, const int* seq_slot,
                             const int* seq_pos0, const int* block_table,
                             int max_pages, int n_kv_heads, int group, TOut* out,
-                            int out_stride, float scale, int window, int max_splits,
+                            int out_stride, float scale, float softcap,
+                            const float* __restrict__ sink, int window, int max_splits,
                             int chunk_pages, float* part, int* counters,
                             int* err_word) {
   using L = AttnSmem<HD>;
@@ -335,7 +336,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int r = quarter * 32 + lane;         // row of the tile
     const int qpos = pos0 + q0 + r;            // absolute position of this row's query
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const float sl2 = scale * 1.4426950408889634f;    // scores in units of log2(e)
+    // scores in units of log2(e); capped scores carry their scale already
+    const float sl2 = CAP ? 1.4426950408889634f : scale * 1.4426950408889634f;
+    const float cap_in = CAP ? scale / softcap : 0.0f;
     constexpr int OC = HD / 2;                 // output columns of this thread
     float acc[OC];
 #pragma unroll
@@ -407,19 +410,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         vis = up & dn;
       }
       // The scale is positive (the launcher sees to it), so the maximum is taken over the raw
-      // scores and scaled once, and the scaling of a score is folded into its exponent.
+      // scores and scaled once, and the scaling of a score is folded into its exponent.  With
+      // a cap, a score is first replaced by softcap * tanh(scale * score / softcap).
       float x[64];
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (all_visible) {
 #pragma unroll
         for (int e = 0; e < 64; ++e) {
           x[e] = __uint_as_float(e < 32 ? v0[e] : v1[e - 32]);
+          if constexpr (CAP) x[e] = nb_softcap(x[e], cap_in, softcap);
           mx4[e & 3] = fmaxf(mx4[e & 3], x[e]);
         }
       } else {
 #pragma unroll
         for (int e = 0; e < 64; ++e) {
-          x[e] = ((vis >> e) & 1ull) ? __uint_as_float(e < 32 ? v0[e] : v1[e - 32]) : -INFINITY;
+          float raw = __uint_as_float(e < 32 ? v0[e] : v1[e - 32]);
+          if constexpr (CAP) raw = nb_softcap(raw, cap_in, softcap);
+          x[e] = ((vis >> e) & 1ull) ? raw : -INFINITY;
           mx4[e & 3] = fmaxf(mx4[e & 3], x[e]);
         }
       }
@@ -514,6 +521,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         float m_all = -INFINITY;
         for (int i = 0; i < n_splits; ++i) m_all = fmaxf(m_all, __ldcg(all + (size_t)i * REC + r));
         const float m_ref = (m_all == -INFINITY) ? 0.0f : m_all;
+        m_run = m_all;
         l_run = 0.0f;
 #pragma unroll
         for (int c = 0; c < OC; ++c) acc[c] = 0.0f;
@@ -536,7 +544,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     }
 
     if (write_out && r < rows_here) {
-      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      float fix = 1.0f;
+      if (sink != nullptr) {
+        // one more term of the denominator, exp(sink_h), with no key and no value; l_run and
+        // the outputs are in units of 2^m_run
+        const float sk = sink[h] * 1.4426950408889634f;
+        const float m_f = fmaxf(m_run, sk);
+        fix = (m_run == -INFINITY) ? 0.0f : nb_exp2(m_run - m_f);
+        l_run = fmaf(l_run, fix, nb_exp2(sk - m_f));
+      }
+      const float inv = l_run > 0.0f ? fix / l_run : 0.0f;
       TOut* dst = out + (size_t)(row0 + q0 + r) * out_stride + (size_t)h * HD + half * OC;
       if constexpr (sizeof(TOut) == 2) {
 #pragma unroll
@@ -584,13 +601,13 @@ int* error_word() {
   return w ? w + NB_ERRW_ATTENTION_PREFILL_TC : nullptr;
 }
 
-template <int HD, typename TOut>
+template <int HD, typename TOut, bool CAP>
 int launch_tc(const void* q, int q_stride, int q_col, int n_rows, const int* cu_rows,
               const int* seq_slot, const int* seq_pos0, const void* k_cache, const void* v_cache,
               long long n_pages, const int* block_table, int max_pages, int n_heads, int n_kv_heads,
-              void* out, int out_stride, float scale, int window, int n_seqs, int max_q_len,
-              int max_splits, int chunk_pages, float* part, int* counters, int append, int k_col,
-              int v_col, cudaStream_t stream) {
+              void* out, int out_stride, float scale, float softcap, const float* sink, int window,
+              int n_seqs, int max_q_len, int max_splits, int chunk_pages, float* part,
+              int* counters, int append, int k_col, int v_col, cudaStream_t stream) {
   using L = AttnSmem<HD>;
   CUtensorMap mq, mk, mv, mn;
   int rc = make_map(&mq, q, n_rows, q_stride, TILE_Q, 64, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
@@ -602,7 +619,7 @@ int launch_tc(const void* q, int q_stride, int q_col, int n_rows, const int* cu_
   if (rc) return rc;
   rc = make_map(&mn, q, n_rows, q_stride, PAGE_TOKENS, 64, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2);
   if (rc) return rc;
-  auto kern = attention_prefill_tc_kernel<HD, TOut>;
+  auto kern = attention_prefill_tc_kernel<HD, TOut, CAP>;
   static bool configured = false;   // per instantiation
   if (!configured) {
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
@@ -611,8 +628,8 @@ int launch_tc(const void* q, int q_stride, int q_col, int n_rows, const int* cu_
   dim3 grid(((max_q_len + TILE_Q - 1) / TILE_Q) * max_splits, n_heads, n_seqs);
   NB_CUDA(nb_launch(kern, grid, dim3(TC_THREADS), (size_t)L::TOTAL, stream, mq, mk, mv, mn, append, k_col,
                     v_col, q_col, cu_rows, seq_slot, seq_pos0, block_table, max_pages, n_kv_heads,
-                    n_heads / n_kv_heads, (TOut*)out, out_stride, scale, window, max_splits,
-                    chunk_pages, part, counters, error_word()));
+                    n_heads / n_kv_heads, (TOut*)out, out_stride, scale, softcap, sink, window,
+                    max_splits, chunk_pages, part, counters, error_word()));
   return 0;
 }
 
@@ -658,13 +675,15 @@ NB_EXPORT int nb_attention_prefill_tc_record(int head_dim) { return 2 * TILE_Q +
 // (sequence, head, tile), zero before the first use; every launch leaves them at zero).
 // append != 0: the rows also hold the step's keys and values at columns k_col / v_col (key/value
 // head after head); every seq_pos0 must then be a multiple of the page size, and the kernel
-// writes them to the cache itself.
-NB_EXPORT int nb_attention_prefill_tc(const void* q, int dtype, int q_stride, int q_col, int n_rows,
+// writes them to the cache itself.  softcap > 0: a score becomes softcap * tanh(score /
+// softcap); sink: fp32 [n_heads] logits of one more term of the softmax's denominator, or null.
+NB_EXPORT int nb_attention_prefill_tc_capped(const void* q, int dtype, int q_stride, int q_col, int n_rows,
                                       const int* cu_rows, const int* seq_slot, const int* seq_pos0,
                                       const void* k_cache, const void* v_cache, int n_pages,
                                       const int* block_table, int max_pages, int page, int n_heads,
                                       int n_kv_heads, int head_dim, void* out, int out_dtype,
-                                      int out_stride, float scale, int window, int n_seqs,
+                                      int out_stride, float scale, float softcap,
+                                      const float* sink, int window, int n_seqs,
                                       int max_q_len, int max_splits, int chunk_pages, float* part,
                                       int* counters, int append, int k_col, int v_col,
                                       cudaStream_t stream) {
@@ -691,13 +710,36 @@ NB_EXPORT int nb_attention_prefill_tc(const void* q, int dtype, int q_stride, in
                  (uintptr_t)out % 16 == 0,
              NB_ERR_UNSUPPORTED, "attention_prefill_tc: operands must be 16-byte aligned");
   int rc = NB_ERR_UNSUPPORTED;
-#define NB_ARGS q, q_stride, q_col, n_rows, cu_rows, seq_slot, seq_pos0, k_cache, v_cache, (long long)n_pages, block_table, max_pages, n_heads, n_kv_heads, out, out_stride, scale, window, n_seqs, max_q_len, max_splits, chunk_pages, part, counters, append, k_col, v_col, stream
-  if (head_dim == 64)
-    rc = out_dtype == NB_F32 ? launch_tc<64, float>(NB_ARGS) : launch_tc<64, bf16>(NB_ARGS);
+#define NB_ARGS q, q_stride, q_col, n_rows, cu_rows, seq_slot, seq_pos0, k_cache, v_cache, (long long)n_pages, block_table, max_pages, n_heads, n_kv_heads, out, out_stride, scale, softcap, sink, window, n_seqs, max_q_len, max_splits, chunk_pages, part, counters, append, k_col, v_col, stream
+  NB_REQUIRE(softcap >= 0.0f, NB_ERR_BAD_ARG, "attention_prefill_tc: a cap is positive, or 0 for none");
+  if (softcap > 0.0f) {
+    if (head_dim == 64)
+      rc = out_dtype == NB_F32 ? launch_tc<64, float, true>(NB_ARGS) : launch_tc<64, bf16, true>(NB_ARGS);
+    else
+      rc = out_dtype == NB_F32 ? launch_tc<128, float, true>(NB_ARGS) : launch_tc<128, bf16, true>(NB_ARGS);
+  } else if (head_dim == 64)
+    rc = out_dtype == NB_F32 ? launch_tc<64, float, false>(NB_ARGS) : launch_tc<64, bf16, false>(NB_ARGS);
   else
-    rc = out_dtype == NB_F32 ? launch_tc<128, float>(NB_ARGS) : launch_tc<128, bf16>(NB_ARGS);
+    rc = out_dtype == NB_F32 ? launch_tc<128, float, false>(NB_ARGS) : launch_tc<128, bf16, false>(NB_ARGS);
 #undef NB_ARGS
   if (rc) return rc;
   NB_CHECK_LAUNCH("attention_prefill_tc");
   return 0;
+}
+
+// The same without cap and sink.
+NB_EXPORT int nb_attention_prefill_tc(const void* q, int dtype, int q_stride, int q_col, int n_rows,
+                                      const int* cu_rows, const int* seq_slot, const int* seq_pos0,
+                                      const void* k_cache, const void* v_cache, int n_pages,
+                                      const int* block_table, int max_pages, int page, int n_heads,
+                                      int n_kv_heads, int head_dim, void* out, int out_dtype,
+                                      int out_stride, float scale, int window, int n_seqs,
+                                      int max_q_len, int max_splits, int chunk_pages, float* part,
+                                      int* counters, int append, int k_col, int v_col,
+                                      cudaStream_t stream) {
+  return nb_attention_prefill_tc_capped(q, dtype, q_stride, q_col, n_rows, cu_rows, seq_slot, seq_pos0,
+                                        k_cache, v_cache, n_pages, block_table, max_pages, page,
+                                        n_heads, n_kv_heads, head_dim, out, out_dtype, out_stride,
+                                        scale, 0.0f, nullptr, window, n_seqs, max_q_len, max_splits,
+                                        chunk_pages, part, counters, append, k_col, v_col, stream);
 }

@@ -435,12 +435,34 @@ class CudaBackend:
                    kv.page, kv.n_kv_heads, kv.head_dim, n_rows,
                    self._stream())
 
-    def attention(self, q_src, q_col, layout, kv, n_heads, out, scale, window=0, append=None):
+    def attention_takes(self, q_src, q_col, layout, kv, n_heads, out, scale) -> bool:
+        """Whether ``attention`` has a kernel with a cap and a sink for these rows: the decode
+        kernel, or the tensor-core kernel for prompts (bf16, heads of 64 or 128)."""
+        if kv.v is None or q_src.dtype != kv.k.dtype:
+            return False
+        code = dtype_code(q_src.dtype)
+        if layout.is_decode:
+            return bool(self.lib.nb_attention_decode_supported(code, kv.head_dim, n_heads,
+                                                               kv.n_kv_heads, kv.page)) and \
+                (q_src.dtype != torch.bfloat16 or (q_src.shape[1] % 8 == 0 and q_col % 2 == 0))
+        return bool(self.use_tcgen05 and scale > 0 and self.lib.nb_attention_prefill_tc_supported(
+            code, kv.head_dim, n_heads, kv.n_kv_heads, kv.page, q_src.shape[1], q_col,
+            dtype_code(out.dtype), out.shape[1]))
+
+    def attention(self, q_src, q_col, layout, kv, n_heads, out, scale, window=0, append=None,
+                  softcap=0.0, sink=None):
         """Causal attention of the packed rows of ``layout`` over the cache ``kv``.
         ``append=(k_col, v_col)``: the rows of ``q_src`` also hold this step's keys and values
         at those columns; they are written to the cache as well (inside the decode kernel and,
         for sequences that start at a page boundary, inside the tensor-core prefill kernel;
-        else by a pass of their own before the attention kernel)."""
+        else by a pass of their own before the attention kernel).  ``softcap`` > 0 replaces a
+        score by ``softcap * tanh(score / softcap)``; ``sink`` (fp32 ``[n_heads]``) adds one
+        term ``exp(sink_h)`` to the softmax's denominator.  With either, the decode kernel and
+        the tensor-core prompt kernel are the only ones here: the caller asks
+        ``attention_takes`` first."""
+        capped = bool(softcap and softcap > 0) or sink is not None
+        if capped and (append or not self.attention_takes(q_src, q_col, layout, kv, n_heads, out, scale)):
+            raise KernelError("attention: no kernel with a cap or a sink takes this shape")
         _check(q_src, "q", kv.k.dtype, 2)
         _check(out, "out", None, 2)
         n_rows = layout.n_rows
@@ -453,6 +475,15 @@ class CudaBackend:
             n_splits = self._decode_splits(n_rows * kv.n_kv_heads, pages, kv, q_src.dtype)
             acc, ml, counters = self._decode_scratch(q_src.device, n_rows, n_heads, kv.n_kv_heads,
                                                      kv.head_dim, n_splits)
+            if capped:
+                self._call("nb_attention_decode_capped", _ptr(q_src), dtype_code(q_src.dtype),
+                           q_src.shape[1], q_col, _ptr(layout.row_slot), _ptr(layout.row_pos),
+                           _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), kv.block_table.shape[1],
+                           kv.page, n_heads, kv.n_kv_heads, kv.head_dim, _ptr(out),
+                           dtype_code(out.dtype), out.shape[1], scale, float(softcap or 0.0),
+                           _ptr(sink), window, n_rows, n_splits, _ptr(acc), _ptr(ml),
+                           _ptr(counters), self._stream())
+                return
             self._call("nb_attention_decode", _ptr(q_src), dtype_code(q_src.dtype),
                        q_src.shape[1], q_col, _ptr(layout.row_slot),
                        _ptr(layout.row_pos), _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table),
@@ -492,12 +523,13 @@ class CudaBackend:
             part = counters = None
             if max_splits > 1:
                 part, counters = self._prefill_scratch(q_src.device, ctas, max_splits, kv.head_dim)
-            self._call("nb_attention_prefill_tc", _ptr(q_src), dtype_code(q_src.dtype),
+            self._call("nb_attention_prefill_tc_capped", _ptr(q_src), dtype_code(q_src.dtype),
                        q_src.shape[1], q_col, q_src.shape[0], _ptr(layout.cu_rows),
                        _ptr(layout.seq_slot), _ptr(layout.seq_pos0), _ptr(kv.k), _ptr(kv.v),
                        kv.k.shape[0], _ptr(kv.block_table), kv.block_table.shape[1], kv.page,
                        n_heads, kv.n_kv_heads, kv.head_dim, _ptr(out), dtype_code(out.dtype),
-                       out.shape[1], scale, window, layout.n_seqs, layout.max_q_len,
+                       out.shape[1], scale, float(softcap or 0.0), _ptr(sink), window,
+                       layout.n_seqs, layout.max_q_len,
                        max_splits, chunk, _ptr(part), _ptr(counters), 1 if fused else 0,
                        append[0] if fused else 0, append[1] if fused else 0, self._stream())
             return
@@ -754,7 +786,8 @@ class CudaBackend:
                    st.stride(0) if st is not None else 0, _ptr(layout.cu_rows),
                    _ptr(layout.seq_slot), _ptr(layout.seq_pos0), _ptr(freq), int(rot_dims),
                    _ptr(q_out), dtype_code(q_out.dtype), _ptr(k_store.k), _ptr(k_store.block_table),
-                   k_store.block_table.shape[1], _ptr(v_store.k), _ptr(v_store.block_table),
+                   k_store.block_table.shape[1],
+                   _ptr(k_store.v if v_store is k_store else v_store.k), _ptr(v_store.block_table),
                    v_store.block_table.shape[1], dtype_code(k_store.k.dtype), k_store.page, n_heads,
                    G, d, dv, layout.n_seqs, layout.max_q_len, fused, self._stream())
         if taps > 1 and not fused:
@@ -791,22 +824,29 @@ class CudaBackend:
 
     def attention_capped(self, q, layout, k_store, v_store, n_heads, sink, out, scale, softcap):
         """Causal attention of the packed rows over the keys of ``k_store`` and the values of
-        ``v_store`` (paged stores of one plane, head sizes ``d`` and ``dv``): scores ``scale *
+        ``v_store`` (paged stores of one plane, head sizes ``d`` and ``dv``; or one store of two
+        planes given twice, which the framework's attention kernels then read): scores ``scale *
         q . k``, with ``softcap`` > 0 replaced by ``softcap * tanh(score / softcap)``; ``sink``:
         fp32 ``[n_heads]`` logits of one more term of the softmax's denominator, or ``None``."""
         _check(q, "q", None, 2)
         _check(out, "out", None, 2)
         n, d, dv = layout.n_rows, k_store.head_dim, v_store.head_dim
         if q.shape != (n, n_heads * d) or out.shape != (n, n_heads * dv) or \
-                k_store.n_kv_heads != v_store.n_kv_heads or k_store.k.dtype != v_store.k.dtype:
+                k_store.n_kv_heads != v_store.n_kv_heads or k_store.k.dtype != v_store.k.dtype or \
+                (v_store is k_store and k_store.v is None):
             raise KernelError("attention_capped: shapes do not agree")
         if sink is not None:
             _check(sink, "sink", torch.float32, 1)
             if sink.numel() != n_heads:
                 raise KernelError("attention_capped: one sink per head")
+        shared = v_store is k_store          # one store of two planes: keys and values of one size
+        if shared and self.attention_takes(q, 0, layout, k_store, n_heads, out, scale):
+            self.attention(q, 0, layout, k_store, n_heads, out, scale, 0, None, softcap, sink)
+            return
+        v_plane = k_store.v if shared else v_store.k
         self._call("nb_attention_capped", _ptr(q), dtype_code(q.dtype), _ptr(layout.row_slot),
                    _ptr(layout.row_pos), _ptr(k_store.k), _ptr(k_store.block_table),
-                   k_store.block_table.shape[1], _ptr(v_store.k), _ptr(v_store.block_table),
+                   k_store.block_table.shape[1], _ptr(v_plane), _ptr(v_store.block_table),
                    v_store.block_table.shape[1], dtype_code(k_store.k.dtype), k_store.page, n_heads,
                    k_store.n_kv_heads, d, dv, _ptr(sink), _ptr(out), dtype_code(out.dtype),
                    float(scale), float(softcap or 0.0), n, self._stream())

@@ -12,6 +12,7 @@ SIGNATURES = {
     "nb_attention_decode_scratch": "iiiiippp",
     "nb_attention_decode": "piiipppppiiiiipiifiiipppiiip",
     "nb_attention_decode_static": "piiipppppiiiiipiifiiip",
+    "nb_attention_decode_capped": "piiipppppiiiiipiiffpiiipppp",
     "nb_attention_decode_cluster_merge": "i",
     "nb_attention_decode_cluster_limit": "",
     "nb_attention_generic": "piiipppppiiiiipiifiip",
@@ -23,6 +24,7 @@ SIGNATURES = {
     "nb_attention_prefill_tc_error": "",
     "nb_attention_prefill_tc_set_wait_budget": "l",
     "nb_attention_prefill_tc": "piiiipppppipiiiiipiifiiiiippiiip",
+    "nb_attention_prefill_tc_capped": "piiiipppppipiiiiipiiffpiiiiippiiip",
     "nb_attention_prefill_tc_record": "i",
     "nb_gemm_simt": "pipipppiiiiip",
     "nb_gemm_skinny": "pippfpipppiiiiip",

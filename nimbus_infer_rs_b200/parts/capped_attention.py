@@ -22,8 +22,9 @@ class CappedAttention(Mixer):
     softcap)``; every earlier token and the token itself are seen; with ``sink`` the softmax's
     denominator has one more term ``exp(sink_h)`` per head, without key or value.
 
-    Storage: two paged stores of one plane (keys; values, which may differ in size) and, in the
-    sequence's state row, the last ``taps - 1`` projected rows (what the convolution of the next
+    Storage: keys and values of one size share a paged store of two planes (the layout of
+    ``causal_attention``, whose decode and tensor-core prompt kernels then run, with cap and
+    sink); of different sizes they take two stores of one plane.  In the sequence's state row, the last ``taps - 1`` projected rows (what the convolution of the next
     tokens reads of the past).
     """
     graph_safe = True
@@ -36,6 +37,7 @@ class CappedAttention(Mixer):
         self.width, self.n_heads, self.n_kv_heads = int(width), int(n_heads), int(n_kv_heads)
         self.head_dim = int(head_dim)
         self.value_dim = int(value_dim) if value_dim else self.head_dim
+        self.one_store = self.value_dim == self.head_dim
         self.scale, self.softcap = float(scale), float(softcap or 0.0)
         self.taps = int(conv or 0)
         if self.n_heads % self.n_kv_heads:
@@ -73,10 +75,10 @@ class CappedAttention(Mixer):
             self.rot_freq = self.rot_freq_host.to(runtime.device)
 
     def cache_request(self):
-        return KVRequest(self.n_kv_heads, self.head_dim, 0, planes=1)
+        return KVRequest(self.n_kv_heads, self.head_dim, 0, planes=2 if self.one_store else 1)
 
     def extra_cache_requests(self):
-        return (KVRequest(self.n_kv_heads, self.value_dim, 0, planes=1),)
+        return () if self.one_store else (KVRequest(self.n_kv_heads, self.value_dim, 0, planes=1),)
 
     def state_request(self):
         return StateRequest(max(self.taps - 1, 0) * self.channels)
@@ -84,7 +86,8 @@ class CappedAttention(Mixer):
     def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
         lay, ops = ctx.layout, ctx.ops
         n, dev, act = lay.n_rows, h.device, ctx.rt.act_dtype
-        keys, values = ctx.kv, ctx.kv_extra[0]
+        keys = ctx.kv
+        values = keys if self.one_store else ctx.kv_extra[0]
         fused = self.proj(ctx, h, out_dtype=torch.float32)
         q = torch.empty((n, self.q_width), device=dev, dtype=act)
         ops.conv_rope_append(fused, 0, self.conv if self.taps > 0 else None, self.taps, ctx.state,

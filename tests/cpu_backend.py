@@ -202,6 +202,11 @@ class CpuBackend:
             state_row.copy_(window[1:].reshape(-1))
         return y
 
+    @staticmethod
+    def _values_of(k_store, v_store):
+        """The plane of values: the second plane when one store holds both."""
+        return k_store.v if v_store is k_store else v_store.k
+
     def conv_rope_append(self, src, col0, w, taps, state, freq, rot_dims, layout, k_store,
                          v_store, n_heads, dv, q_out):
         d, G = k_store.head_dim, k_store.n_kv_heads
@@ -230,7 +235,7 @@ class CpuBackend:
                                state[slot] if taps > 1 else None, C)
             q_out[r] = turn(y[:qw].view(n_heads, d), pos).reshape(-1).to(q_out.dtype)
             self._entry(k_store, k_store.k, slot, pos)[:] = turn(y[qw:qw + kw].view(G, d), pos).to(k_store.k.dtype)
-            self._entry(v_store, v_store.k, slot, pos)[:] = y[qw + kw:].view(G, dv).to(v_store.k.dtype)
+            self._entry(v_store, self._values_of(k_store, v_store), slot, pos)[:] = y[qw + kw:].view(G, dv).to(v_store.k.dtype)
 
     def conv_act(self, src, col0, w, bias, taps, act, state, layout, out_f32, out_act=None):
         C = out_f32.shape[1]
@@ -258,7 +263,7 @@ class CpuBackend:
                 continue
             pos = int(layout.row_pos[r])
             keys = torch.stack([self._entry(k_store, k_store.k, slot, j).float() for j in range(pos + 1)])
-            vals = torch.stack([self._entry(v_store, v_store.k, slot, j).float() for j in range(pos + 1)])
+            vals = torch.stack([self._entry(v_store, self._values_of(k_store, v_store), slot, j).float() for j in range(pos + 1)])
             qr = q[r].float().view(n_heads, d)
             for h in range(n_heads):
                 s = (keys[:, h // group] @ qr[h]) * scale
@@ -449,7 +454,11 @@ class CpuBackend:
             kv.k[page, :, pos % kv.page, :] = src[r, k_col:k_col + w].view(kv.n_kv_heads, kv.head_dim)
             kv.v[page, :, pos % kv.page, :] = src[r, v_col:v_col + w].view(kv.n_kv_heads, kv.head_dim)
 
-    def attention(self, q_src, q_col, layout, kv, n_heads, out, scale, window=0, append=None):
+    def attention_takes(self, q_src, q_col, layout, kv, n_heads, out, scale) -> bool:
+        return kv.v is not None
+
+    def attention(self, q_src, q_col, layout, kv, n_heads, out, scale, window=0, append=None,
+                  softcap=0.0, sink=None):
         if append:
             self.kv_append(q_src, append[0], append[1], layout.row_slot, layout.row_pos, kv,
                            layout.n_rows)
@@ -469,7 +478,12 @@ class CpuBackend:
             q = q_src[r, q_col:q_col + n_heads * hd].float().view(n_heads, hd)
             for h in range(n_heads):
                 s = (keys[:, h // group] @ q[h]) * scale
-                p = torch.softmax(s, dim=0)
+                if softcap and softcap > 0:
+                    s = softcap * torch.tanh(s / softcap)
+                if sink is not None:
+                    p = torch.softmax(torch.cat([s, sink[h].float().view(1)]), dim=0)[:-1]
+                else:
+                    p = torch.softmax(s, dim=0)
                 out[r, h * hd:(h + 1) * hd] = (p @ vals[:, h // group]).to(out.dtype)
 
     def argmax(self, logits, out):

@@ -83,10 +83,13 @@ def test_gates_casts_and_the_gated_norm(ops, dtype):
 
 # ----------------------------------------------------------------------------- storage helpers
 def _stores(dtype, G, d, dv, n_state, tokens, n_slots=None, fill=None):
-    cache = SequenceCache({0: KVRequest(G, d, 0, 1)}, {0: StateRequest(n_state)} if n_state else {},
+    """Keys and values of one size share a store of two planes, as in the part; else a store each."""
+    shared = d == dv
+    cache = SequenceCache({0: KVRequest(G, d, 0, 2 if shared else 1)},
+                          {0: StateRequest(n_state)} if n_state else {},
                           cache_tokens=tokens, max_seq_len=tokens, dtype=ACT[dtype],
                           device=torch.device(DEV), n_slots=n_slots,
-                          extra_kv_requests={(0, 0): KVRequest(G, dv, 0, 1)})
+                          extra_kv_requests={} if shared else {(0, 0): KVRequest(G, dv, 0, 1)})
     if fill is not None:           # what an earlier owner of the pages left behind
         for g in cache.groups:
             g.storage.fill_(fill)
@@ -111,7 +114,8 @@ def _attention(ops, dtype, q, k, v, conv, rot, scale, softcap, sink, pieces, fil
     for n in pieces:
         cache.reserve([(slot, n)])
         lay = build_layout([(slot, [0] * n, [])], [at], DEV)
-        keys, values = cache.layer_kv(0), cache.layer_kv_extra(0)[0]
+        keys = cache.layer_kv(0)
+        values = keys if d == dv else cache.layer_kv_extra(0)[0]
         qo = torch.empty(n, H * d, device=DEV, dtype=ACT[dtype])
         ops.conv_rope_append(fused[at:at + n].contiguous(), 0, w, taps, cache.layer_state(0), freq, dims,
                              lay, keys, values, H, dv, qo)
@@ -150,6 +154,11 @@ def _plain_attention(q, k, v, conv, rot, scale, softcap, sink):
     dict(H=2, G=1, d=3, dv=1, taps=0, cap=2.0, rot=dict(dims=2, base=10.0)),
     dict(H=4, G=1, d=64, dv=64, taps=4, cap=0.0, scale=0.04, rot=dict(dims=64, base=1e4)),
     dict(H=2, G=2, d=33, dv=130, taps=7, cap=50.0, rot=dict(dims=32, base=500.0, scaling=dict(factor=4.0, low=1.0, high=4.0, original=64))),
+    # head sizes that the tensor-core prompt kernel and the decode kernel of plain attention take
+    dict(H=6, G=2, d=64, dv=64, taps=3, cap=4.0, scale=0.09, rot=dict(dims=32, base=300.0)),
+    dict(H=4, G=4, d=128, dv=128, taps=2, cap=12.0, scale=0.05, rot=dict(dims=128, base=1e4)),
+    dict(H=8, G=1, d=128, dv=128, taps=0, cap=0.0, scale=0.06, rot=None),
+    dict(H=2, G=1, d=64, dv=128, taps=4, cap=6.0, scale=0.1, rot=dict(dims=64, base=1e3)),
 ])
 def test_attention_whole_in_portions_and_token_by_token(ops, dtype, case):
     T, H, G, d, dv = 200, case["H"], case["G"], case["d"], case["dv"]
@@ -163,18 +172,19 @@ def test_attention_whole_in_portions_and_token_by_token(ops, dtype, case):
         _close(got, ref, TOL[dtype], f"{case} in {len(pieces)} pieces")
 
 
+@pytest.mark.parametrize("d,dv", [(16, 8), (64, 64)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_a_query_that_points_at_one_far_key(ops, dtype):
+def test_a_query_that_points_at_one_far_key(ops, dtype, d, dv):
     """700 tokens; every query points along one direction that only one key, far back and just
     before a page's end, shares: its value carries nearly all the weight at every later
     position, in a prompt, across a portion's start and decoded alone."""
-    T, d, far = 700, 16, 63
+    T, far = 700, 63
     a = torch.zeros(d)
     a[3] = 1.0
     k = _rnd(T, 1, d, seed=9)
     k[:, 0, 3] = 0.0                         # everyone else is orthogonal to `a`
     k[far, 0] = a * 4.0
-    v = _rnd(T, 1, 8, seed=10)
+    v = _rnd(T, 1, dv, seed=10)
     q = (a * 5.0).repeat(T, 2, 1)
     ref = _plain_attention(q, k, v, None, None, 1.0, 0.0, None)
     assert float((ref[far + 200, 0] - v[far, 0].double()).abs().max()) < 1e-4    # it stands out
@@ -188,22 +198,27 @@ def test_a_query_that_points_at_one_far_key(ops, dtype):
     _close(got, capped, TOL[dtype], "far key under a cap")
 
 
+@pytest.mark.parametrize("d", [8, 64, 128])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_first_tokens_and_a_sink_that_takes_everything(ops, dtype):
-    T, H, d = 70, 2, 8
-    q, k, v = _rnd(T, H, d, seed=1), _rnd(T, 1, d, seed=2), _rnd(T, 1, d, seed=3)
+def test_first_tokens_and_a_sink_that_takes_everything(ops, dtype, d):
+    T, H = 70, 2
+    # exact in bfloat16, so that the cap's steep middle does not magnify the inputs' rounding
+    q, k, v = (_rnd(T, n, d, seed=i).bfloat16().float() for i, n in ((1, H), (2, 1), (3, 1)))
     big = torch.tensor([40.0, -40.0])
-    ref = _plain_attention(q, k, v, None, None, 0.5, 0.0, big)
+    scale = 0.5 * math.sqrt(8 / d)
+    ref = _plain_attention(q, k, v, None, None, scale, 0.0, big)
     assert float(ref[:, 0].abs().max()) < 1e-10 and float(ref[:, 1].abs().max()) > 0.1
     for pieces in ([T], [1] * T):
-        got = _attention(ops, dtype, q, k, v, None, None, 0.5, 0.0, big, pieces)
+        got = _attention(ops, dtype, q, k, v, None, None, scale, 0.0, big, pieces)
         _close(got, ref, TOL[dtype], "a sink of +40 and one of -40")
     # the sink is neither scaled nor capped: under a cap of 1 a sink of 3 still outweighs a key
     small = torch.tensor([3.0, 3.0])
-    ref = _plain_attention(q * 50, k, v, None, None, 0.5, 1.0, small)
-    got = _attention(ops, dtype, q * 50, k, v, None, None, 0.5, 1.0, small, [3, 67])
-    _close(got, ref, TOL[dtype], "sink beside capped scores")
-    first = _plain_attention(q[:1] * 50, k[:1], v[:1], None, None, 0.5, 1.0, small)
+    ref = _plain_attention(q * 64, k, v, None, None, scale, 1.0, small)
+    assert float((ref - _plain_attention(q * 64, k, v, None, None, scale, 1.0, small * 0)).abs().max()) > 0.05
+    for pieces in ([3, 67], [1] * T):
+        got = _attention(ops, dtype, q * 64, k, v, None, None, scale, 1.0, small, pieces)
+        _close(got, ref, TOL[dtype], "sink beside capped scores")
+    first = _plain_attention(q[:1] * 64, k[:1], v[:1], None, None, scale, 1.0, small)
     _close(got[:1], first, TOL[dtype], "the first token sees itself and the sink")
 
 

@@ -184,10 +184,12 @@ def test_every_run_of_a_repeated_layer_has_storage_of_its_own(models, cpu_backen
     e = _engine(models, "A")
     kv, st = e.model.storage_requests()
     extra = e.model.extra_storage_requests()
-    # six runs: pairs at entries 0, 2, 4 keep keys and (wider) values; every run keeps state
-    assert sorted(kv) == [0, 2, 4] and sorted(extra) == [(0, 0), (2, 0), (4, 0)]
+    # six runs: the pair at entry 0 keeps keys and (wider) values in a store each, the pair at
+    # entries 2 and 4 keys and values of one size in one store of two planes; every run keeps state
+    assert sorted(kv) == [0, 2, 4] and sorted(extra) == [(0, 0)]
     assert sorted(st) == [0, 1, 2, 3, 4, 5]
     assert kv[0].head_dim == 12 and extra[(0, 0)].head_dim == 20 and kv[0].planes == 1
+    assert kv[2].head_dim == 16 and kv[2].planes == 2 and kv[4] == kv[2]
     # the pair's row: the attention's last two projected rows, the scan's last four inputs, its state
     assert st[0].n_elements == 2 * (48 + 24 + 40) + 4 * 40 + 40 * 5
     assert st[1].n_elements == 3 * 10 * 14 and st[1] == st[3]
