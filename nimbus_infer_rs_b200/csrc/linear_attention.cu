@@ -8,16 +8,26 @@
 //
 // A CTA takes one sequence, one head and a block of value columns, and walks the step's tokens
 // in order.  A value column's d state numbers sit in the registers of LANES neighbouring lanes
-// (d / LANES each, at most 32); a token costs a thread two multiply-adds per state number, and
-// the lanes' parts of o are added up by shuffles.  Tokens are staged in chunks of 16: the
-// chunk's activated queries and keys of the head and the values of the CTA's columns go to
-// shared memory in one cooperative pass.
+// (16 each, in groups of four consecutive key channels, so that a lane reads its part of a
+// token's key and query as 16-byte pieces and the lanes of a column read consecutive pieces);
+// a token costs a thread two multiply-adds per state number, and the lanes' parts of o are
+// added up by shuffles.  Tokens are staged in chunks of 16 through two buffers of shared
+// memory: while one chunk is walked, asynchronous copies bring the next one's queries and keys
+// of the head and values of the CTA's columns; the activation is applied in place once the
+// chunk has landed.  Rows of the buffers are LANES * 16 wide; what lies beyond d stays zero, so
+// that the walk needs no bounds.  The columns of a CTA are chosen by the launcher so that the
+// grid fills the GPU.
 #include "common.cuh"
 
 namespace {
 
 constexpr int LA_CHUNK = 16;
-constexpr int LA_PER = 32;        // state numbers a thread holds
+constexpr int LA_PER = 16;        // state numbers a thread holds
+
+__device__ __forceinline__ void la_copy4(float* dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
+}
 
 template <int LANES>
 __global__ void __launch_bounds__(256)
@@ -27,61 +37,85 @@ linear_attention_kernel(const float* src, int stride, int col_q, int col_k, int 
                         int cols_per_cta, float* out) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
-  extern __shared__ float la_smem[];
-  float* q_s = la_smem;                       // [CHUNK][d]
-  float* k_s = q_s + LA_CHUNK * d;            // [CHUNK][d]
-  float* v_s = k_s + LA_CHUNK * d;            // [CHUNK][cols_per_cta]
+  constexpr int DS = LANES * LA_PER;          // a staged row of queries or keys
+  extern __shared__ __align__(16) float la_smem[];
+  const int buf_floats = LA_CHUNK * (2 * DS + cols_per_cta);   // [CHUNK][DS] q, k; [CHUNK][cols] v
   const int s = blockIdx.z, h = blockIdx.y;
   const int slot = seq_slot[s];
   const int row0 = cu_rows[s], n_q = cu_rows[s + 1] - row0;
   if (slot < 0 || n_q <= 0) return;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, n_threads = blockDim.x;
   const int col_local = tid / LANES, part = tid % LANES;
   const int j0 = blockIdx.x * cols_per_cta;
   const int j = j0 + col_local;
   const bool live = col_local < cols_per_cta && j < dv;
-  const int per = (d + LANES - 1) / LANES;    // key channels of this lane: part*per .. +per
-  const int i0 = part * per;
+  const int n_cols = min(cols_per_cta, dv - j0);
+  // state number a of this lane is key channel chan(a)
+  auto chan = [&](int a) { return (a >> 2) * (LANES * 4) + part * 4 + (a & 3); };
   float S[LA_PER];
   float* st = state + (size_t)slot * state_stride + (size_t)h * d * dv;
 #pragma unroll
-  for (int a = 0; a < LA_PER; ++a) {
-    const int i = i0 + a;
-    S[a] = (live && a < per && i < d) ? st[(size_t)i * dv + j] : 0.0f;
-  }
+  for (int a = 0; a < LA_PER; ++a) S[a] = (live && chan(a) < d) ? st[(size_t)chan(a) * dv + j] : 0.0f;
   const float w = decay[h];
-  const int n_cols = min(cols_per_cta, dv - j0);
+  for (int i = tid; i < 2 * buf_floats; i += n_threads) la_smem[i] = 0.0f;
+  __syncthreads();
 
-  for (int t0 = 0; t0 < n_q; t0 += LA_CHUNK) {
+  auto issue = [&](int t0, float* buf) {
     const int nt = min(LA_CHUNK, n_q - t0);
-    __syncthreads();
-    for (int e = tid; e < nt * d; e += blockDim.x) {
+    float* q_s = buf;
+    float* k_s = q_s + LA_CHUNK * DS;
+    float* v_s = k_s + LA_CHUNK * DS;
+    for (int e = tid; e < nt * d; e += n_threads) {
       const int t = e / d, i = e - t * d;
       const float* row = src + (size_t)(row0 + t0 + t) * stride;
-      q_s[e] = nb_apply_act(row[col_q + h * d + i], act);
-      k_s[e] = nb_apply_act(row[col_k + h * d + i], act);
+      la_copy4(q_s + t * DS + i, row + col_q + h * d + i);
+      la_copy4(k_s + t * DS + i, row + col_k + h * d + i);
     }
-    for (int e = tid; e < nt * n_cols; e += blockDim.x) {
+    for (int e = tid; e < nt * n_cols; e += n_threads) {
       const int t = e / n_cols, c = e - t * n_cols;
-      v_s[t * cols_per_cta + c] =
-          nb_apply_act(src[(size_t)(row0 + t0 + t) * stride + col_v + h * dv + j0 + c], act);
+      la_copy4(v_s + t * cols_per_cta + c, src + (size_t)(row0 + t0 + t) * stride + col_v + h * dv + j0 + c);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+
+  issue(0, la_smem);
+  int which = 0;
+  for (int t0 = 0; t0 < n_q; t0 += LA_CHUNK, which ^= 1) {
+    const int nt = min(LA_CHUNK, n_q - t0);
+    float* q_s = la_smem + which * buf_floats;
+    float* k_s = q_s + LA_CHUNK * DS;
+    float* v_s = k_s + LA_CHUNK * DS;
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();     // the chunk is in; everyone is done with the other buffer
+    if (t0 + LA_CHUNK < n_q) issue(t0 + LA_CHUNK, la_smem + (which ^ 1) * buf_floats);
+    if (act != NB_ACT_NONE) {
+      for (int e = tid; e < nt * d; e += n_threads) {
+        const int t = e / d, i = e - t * d;
+        q_s[t * DS + i] = nb_apply_act(q_s[t * DS + i], act);
+        k_s[t * DS + i] = nb_apply_act(k_s[t * DS + i], act);
+      }
+      for (int e = tid; e < nt * n_cols; e += n_threads) {
+        const int t = e / n_cols, c = e - t * n_cols;
+        v_s[t * cols_per_cta + c] = nb_apply_act(v_s[t * cols_per_cta + c], act);
+      }
     }
     __syncthreads();
     for (int t = 0; t < nt; ++t) {
       const float v = live ? v_s[t * cols_per_cta + col_local] : 0.0f;
-      const float* qt = q_s + t * d + i0;
-      const float* kt = k_s + t * d + i0;
+      const float4* qt = reinterpret_cast<const float4*>(q_s + t * DS + part * 4);
+      const float4* kt = reinterpret_cast<const float4*>(k_s + t * DS + part * 4);
       float o0 = 0.0f, o1 = 0.0f;
 #pragma unroll
-      for (int a = 0; a < LA_PER; a += 2) {
-        if (a < per && i0 + a < d) {
-          S[a] = fmaf(w, S[a], kt[a] * v);
-          o0 = fmaf(S[a], qt[a], o0);
-        }
-        if (a + 1 < per && i0 + a + 1 < d) {
-          S[a + 1] = fmaf(w, S[a + 1], kt[a + 1] * v);
-          o1 = fmaf(S[a + 1], qt[a + 1], o1);
-        }
+      for (int g = 0; g < LA_PER / 4; ++g) {
+        const float4 k4 = kt[g * LANES], q4 = qt[g * LANES];
+        S[4 * g] = fmaf(w, S[4 * g], k4.x * v);
+        o0 = fmaf(S[4 * g], q4.x, o0);
+        S[4 * g + 1] = fmaf(w, S[4 * g + 1], k4.y * v);
+        o1 = fmaf(S[4 * g + 1], q4.y, o1);
+        S[4 * g + 2] = fmaf(w, S[4 * g + 2], k4.z * v);
+        o0 = fmaf(S[4 * g + 2], q4.z, o0);
+        S[4 * g + 3] = fmaf(w, S[4 * g + 3], k4.w * v);
+        o1 = fmaf(S[4 * g + 3], q4.w, o1);
       }
       float o = o0 + o1;
 #pragma unroll
@@ -92,10 +126,8 @@ linear_attention_kernel(const float* src, int stride, int col_q, int col_k, int 
   }
   if (live)
 #pragma unroll
-    for (int a = 0; a < LA_PER; ++a) {
-      const int i = i0 + a;
-      if (a < per && i < d) st[(size_t)i * dv + j] = S[a];
-    }
+    for (int a = 0; a < LA_PER; ++a)
+      if (chan(a) < d) st[(size_t)chan(a) * dv + j] = S[a];
 }
 
 }  // namespace
@@ -118,11 +150,21 @@ NB_EXPORT int nb_linear_attention(const float* src, int stride, int col_q, int c
              NB_ERR_BAD_ARG, "linear_attention: bad sizes heads=%d d=%d dv=%d", n_heads, d, dv);
   int lanes = 1;
   while (lanes * LA_PER < d) lanes *= 2;                 // 1, 2, 4, ..., 32
-  const int max_cols = 256 / lanes;
-  const int cols = dv < max_cols ? dv : max_cols;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    NB_CUDA(cudaGetDevice(&dev));
+    NB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  // as many columns a CTA as 256 threads hold; fewer (down to a warp's worth) while the grid
+  // would not give every SM two CTAs
+  int cols = 256 / lanes;
+  if (cols > dv) cols = dv;
+  while (cols * lanes > 32 && (long long)((dv + cols - 1) / cols) * n_heads * n_seqs < 2LL * sms)
+    cols = (cols + 1) / 2;
   const int threads = ((cols * lanes + 31) / 32) * 32;
   const dim3 grid((dv + cols - 1) / cols, n_heads, n_seqs);
-  const size_t smem = (size_t)LA_CHUNK * (2 * d + cols) * sizeof(float);
+  const size_t smem = (size_t)2 * LA_CHUNK * (2 * lanes * LA_PER + cols) * sizeof(float);
 #define NB_LA(L_)                                                                                 \
   case L_: {                                                                                      \
     auto kern = linear_attention_kernel<L_>;                                                      \

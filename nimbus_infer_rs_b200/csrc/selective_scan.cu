@@ -7,12 +7,13 @@
 // with B and C (N numbers each) shared by all channels of a token.  All of it fp32; the state of
 // a sequence lives in its fixed-size state row ([channels][N]) between steps.
 //
-// A CTA takes 128 channels of one sequence and walks the step's tokens in order; a thread owns
-// a channel with its N state numbers and its row of A in registers.  Tokens are staged in
-// chunks of 16: B and C of the chunk and the chunk's step sizes, inputs and gates of the CTA's
-// channels go to shared memory in one cooperative pass (softplus applied there), then every
-// thread runs the 16 tokens out of shared memory.  Results are written as they come (a warp's
-// stores of one token are consecutive).
+// A CTA takes a block of channels of one sequence and walks the step's tokens in order.  A
+// channel's N state numbers and its row of A sit in the registers of LANES neighbouring lanes
+// (NPER each), so that a model with a small state still fills the GPU with CTAs; the lanes'
+// parts of y are added up by shuffles.  Tokens are staged in chunks of 16 through two buffers of
+// shared memory: while the threads run one chunk, asynchronous copies bring the next one's B
+// and C, step sizes, inputs and gates.  The step sizes' softplus is applied once per token and
+// channel, in place, before the chunk is used.
 #include "common.cuh"
 
 namespace {
@@ -24,7 +25,12 @@ __device__ __forceinline__ float ss_softplus(float x) {
   return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x)));
 }
 
-template <int NMAX, typename TOut>
+__device__ __forceinline__ void ss_copy4(float* dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
+}
+
+template <int NPER, int LANES, typename TOut>
 __global__ void __launch_bounds__(SS_THREADS)
 selective_scan_kernel(const float* x, const float* low, int low_stride, int col_b, int col_c,
                       const float* dt_lin, const float* __restrict__ dt_bias,
@@ -33,88 +39,119 @@ selective_scan_kernel(const float* x, const float* low, int low_stride, int col_
                       const int* cu_rows, const int* seq_slot, int inner, int N, TOut* out) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
+  constexpr int CH = SS_THREADS / LANES;               // channels of a CTA
   extern __shared__ float ss_smem[];
-  float* bc_s = ss_smem;                               // [CHUNK][2N]
-  float* dt_s = bc_s + SS_CHUNK * 2 * N;               // [CHUNK][THREADS]
-  float* x_s = dt_s + SS_CHUNK * SS_THREADS;
-  float* z_s = x_s + SS_CHUNK * SS_THREADS;
+  const int buf_floats = SS_CHUNK * (2 * N + 3 * CH);  // [CHUNK][2N] B|C, then dt, x, z [CHUNK][CH]
   const int s = blockIdx.y;
   const int slot = seq_slot[s];
   const int row0 = cu_rows[s], n_q = cu_rows[s + 1] - row0;
   if (slot < 0 || n_q <= 0) return;     // rows of a sequence that has ended keep what they held
-  const int c0 = blockIdx.x * SS_THREADS, tid = threadIdx.x;
-  const int c = c0 + tid;
+  const int tid = threadIdx.x;
+  const int cl = tid / LANES, part = tid % LANES;
+  const int c0 = blockIdx.x * CH, c = c0 + cl;
+  const int n0 = part * NPER;
   const bool live = c < inner;
-  float S[NMAX], A[NMAX];
+  const int n_ch = min(CH, inner - c0);
+  float S[NPER], A[NPER];
   float* st = state + (size_t)slot * state_stride + (size_t)c * N;
 #pragma unroll
-  for (int n = 0; n < NMAX; ++n) {
-    S[n] = (live && n < N) ? st[n] : 0.0f;
-    A[n] = (live && n < N) ? -expf(a_log[(size_t)c * N + n]) : 0.0f;
+  for (int a = 0; a < NPER; ++a) {
+    const bool has = live && n0 + a < N;
+    S[a] = has ? st[n0 + a] : 0.0f;
+    A[a] = has ? -expf(a_log[(size_t)c * N + n0 + a]) : 0.0f;
   }
-  const float bias = live ? dt_bias[c] : 0.0f, dsk = live ? d_skip[c] : 0.0f;
+  const float dsk = live ? d_skip[c] : 0.0f;
 
-  for (int t0 = 0; t0 < n_q; t0 += SS_CHUNK) {
+  auto issue = [&](int t0, float* buf) {
     const int nt = min(SS_CHUNK, n_q - t0);
-    __syncthreads();
+    float* bc_s = buf;
+    float* dt_s = buf + SS_CHUNK * 2 * N;
+    float* x_s = dt_s + SS_CHUNK * CH;
+    float* z_s = x_s + SS_CHUNK * CH;
     for (int i = tid; i < nt * 2 * N; i += SS_THREADS) {
       const int t = i / (2 * N), j = i - t * 2 * N;
-      bc_s[i] = low[(size_t)(row0 + t0 + t) * low_stride + (j < N ? col_b + j : col_c + j - N)];
+      ss_copy4(bc_s + i, low + (size_t)(row0 + t0 + t) * low_stride + (j < N ? col_b + j : col_c + j - N));
     }
-    if (live)
-      for (int t = 0; t < nt; ++t) {
-        const size_t r = row0 + t0 + t;
-        dt_s[t * SS_THREADS + tid] = ss_softplus(dt_lin[r * inner + c] + bias);
-        x_s[t * SS_THREADS + tid] = x[r * inner + c];
-        z_s[t * SS_THREADS + tid] = zsrc[r * z_stride + z_col + c];
-      }
+    for (int i = tid; i < nt * CH; i += SS_THREADS) {
+      const int t = i / CH, k = i - t * CH;
+      if (k >= n_ch) continue;
+      const size_t r = row0 + t0 + t;
+      ss_copy4(dt_s + i, dt_lin + r * inner + c0 + k);
+      ss_copy4(x_s + i, x + r * inner + c0 + k);
+      ss_copy4(z_s + i, zsrc + r * z_stride + z_col + c0 + k);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+
+  issue(0, ss_smem);
+  int which = 0;
+  for (int t0 = 0; t0 < n_q; t0 += SS_CHUNK, which ^= 1) {
+    const int nt = min(SS_CHUNK, n_q - t0);
+    float* buf = ss_smem + which * buf_floats;
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();     // the chunk is in; everyone is done with the other buffer
+    if (t0 + SS_CHUNK < n_q) issue(t0 + SS_CHUNK, ss_smem + (which ^ 1) * buf_floats);
+    float* bc_s = buf;
+    float* dt_s = buf + SS_CHUNK * 2 * N;
+    const float* x_s = dt_s + SS_CHUNK * CH;
+    const float* z_s = x_s + SS_CHUNK * CH;
+    for (int i = tid; i < nt * CH; i += SS_THREADS) {
+      const int k = i % CH;
+      if (k < n_ch) dt_s[i] = ss_softplus(dt_s[i] + dt_bias[c0 + k]);
+    }
     __syncthreads();
-    if (!live) continue;
+    // (a warp's channels beyond the last one walk along on whatever the buffer holds: the
+    // shuffles below want every lane, and nothing of theirs is written)
     for (int t = 0; t < nt; ++t) {
-      const float dt = dt_s[t * SS_THREADS + tid], xv = x_s[t * SS_THREADS + tid];
-      const float z = z_s[t * SS_THREADS + tid];
+      const float dt = dt_s[t * CH + cl], xv = x_s[t * CH + cl];
       const float dx = dt * xv;
-      const float* B = bc_s + t * 2 * N;
+      const float* B = bc_s + t * 2 * N + n0;
       const float* Cv = B + N;
       float y0 = 0.0f, y1 = 0.0f;
 #pragma unroll
-      for (int n = 0; n < NMAX; n += 2) {
-        if (n < N) {
-          S[n] = fmaf(expf(dt * A[n]), S[n], dx * B[n]);
-          y0 = fmaf(S[n], Cv[n], y0);
+      for (int a = 0; a < NPER; a += 2) {
+        if (n0 + a < N) {
+          S[a] = fmaf(expf(dt * A[a]), S[a], dx * B[a]);
+          y0 = fmaf(S[a], Cv[a], y0);
         }
-        if (n + 1 < N) {
-          S[n + 1] = fmaf(expf(dt * A[n + 1]), S[n + 1], dx * B[n + 1]);
-          y1 = fmaf(S[n + 1], Cv[n + 1], y1);
+        if (a + 1 < NPER && n0 + a + 1 < N) {
+          S[a + 1] = fmaf(expf(dt * A[a + 1]), S[a + 1], dx * B[a + 1]);
+          y1 = fmaf(S[a + 1], Cv[a + 1], y1);
         }
       }
-      const float y = fmaf(dsk, xv, y0 + y1);
-      out[(size_t)(row0 + t0 + t) * inner + c] = nb_from_f32<TOut>(y * nb_silu(z));
+      float y = y0 + y1;
+#pragma unroll
+      for (int m = LANES / 2; m > 0; m >>= 1) y += __shfl_xor_sync(0xffffffffu, y, m);
+      if (part == 0 && live) {
+        y = fmaf(dsk, xv, y);
+        out[(size_t)(row0 + t0 + t) * inner + c] = nb_from_f32<TOut>(y * nb_silu(z_s[t * CH + cl]));
+      }
     }
   }
   if (live)
 #pragma unroll
-    for (int n = 0; n < NMAX; ++n)
-      if (n < N) st[n] = S[n];
+    for (int a = 0; a < NPER; ++a)
+      if (n0 + a < N) st[n0 + a] = S[a];
 }
 
-template <int NMAX>
+template <int NPER, int LANES>
 int launch_scan(const float* x, const float* low, int low_stride, int col_b, int col_c,
                 const float* dt_lin, const float* dt_bias, const float* a_log, const float* d_skip,
                 const float* z, int z_stride, int z_col, float* state, int state_stride,
                 const int* cu_rows, const int* seq_slot, int inner, int N, void* out, int out_dtype,
                 int n_seqs, cudaStream_t stream) {
-  const dim3 grid((inner + SS_THREADS - 1) / SS_THREADS, n_seqs);
-  const size_t smem = (size_t)(SS_CHUNK * 2 * N + 3 * SS_CHUNK * SS_THREADS) * sizeof(float);
+  constexpr int CH = SS_THREADS / LANES;
+  const dim3 grid((inner + CH - 1) / CH, n_seqs);
+  const size_t smem = (size_t)2 * SS_CHUNK * (2 * N + 3 * CH) * sizeof(float);
   if (out_dtype == NB_F32) {
-    auto kern = selective_scan_kernel<NMAX, float>;
+    auto kern = selective_scan_kernel<NPER, LANES, float>;
     if (smem > 48 * 1024)
       NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     NB_CUDA(nb_launch_serial(kern, grid, dim3(SS_THREADS), smem, stream, x, low, low_stride, col_b,
                              col_c, dt_lin, dt_bias, a_log, d_skip, z, z_stride, z_col, state,
                              state_stride, cu_rows, seq_slot, inner, N, (float*)out));
   } else {
-    auto kern = selective_scan_kernel<NMAX, __nv_bfloat16>;
+    auto kern = selective_scan_kernel<NPER, LANES, __nv_bfloat16>;
     if (smem > 48 * 1024)
       NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     NB_CUDA(nb_launch_serial(kern, grid, dim3(SS_THREADS), smem, stream, x, low, low_stride, col_b,
@@ -143,17 +180,18 @@ NB_EXPORT int nb_selective_scan(const float* x, const float* low, int low_stride
   NB_REQUIRE(inner > 0 && nb_selective_scan_supported(n_state) && n_seqs <= 65535 &&
                  (out_dtype == NB_F32 || out_dtype == NB_BF16) && state != nullptr,
              NB_ERR_BAD_ARG, "selective_scan: bad sizes inner=%d state=%d", inner, n_state);
-#define NB_SS(NMAX_)                                                                              \
-  rc = launch_scan<NMAX_>(x, low, low_stride, col_b, col_c, dt_lin, dt_bias, a_log, d_skip, z,    \
-                          z_stride, z_col, state, state_stride, cu_rows, seq_slot, inner,         \
-                          n_state, out, out_dtype, n_seqs, stream)
+#define NB_SS(NPER_, LANES_)                                                                      \
+  rc = launch_scan<NPER_, LANES_>(x, low, low_stride, col_b, col_c, dt_lin, dt_bias, a_log,       \
+                                  d_skip, z, z_stride, z_col, state, state_stride, cu_rows,       \
+                                  seq_slot, inner, n_state, out, out_dtype, n_seqs, stream)
   int rc;
-  if (n_state <= 8) NB_SS(8);
-  else if (n_state <= 16) NB_SS(16);
-  else if (n_state <= 32) NB_SS(32);
-  else if (n_state <= 64) NB_SS(64);
-  else if (n_state <= 128) NB_SS(128);
-  else NB_SS(256);
+  if (n_state <= 4) NB_SS(4, 1);
+  else if (n_state <= 8) NB_SS(4, 2);
+  else if (n_state <= 16) NB_SS(4, 4);
+  else if (n_state <= 32) NB_SS(4, 8);
+  else if (n_state <= 64) NB_SS(4, 16);
+  else if (n_state <= 128) NB_SS(4, 32);
+  else NB_SS(8, 32);
 #undef NB_SS
   if (rc) return rc;
   NB_CHECK_LAUNCH("selective_scan");
