@@ -29,6 +29,11 @@ __device__ __forceinline__ void la_copy4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
 }
 
+__device__ __forceinline__ void la_copy16(float* dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src) : "memory");
+}
+
 template <int LANES>
 __global__ void __launch_bounds__(256)
 linear_attention_kernel(const float* src, int stride, int col_q, int col_k, int col_v, int act,
@@ -60,20 +65,43 @@ linear_attention_kernel(const float* src, int stride, int col_q, int col_k, int 
   for (int i = tid; i < 2 * buf_floats; i += n_threads) la_smem[i] = 0.0f;
   __syncthreads();
 
+  // 16-byte copies where every piece starts on a 16-byte boundary on both sides
+  const bool wide_qk = (d % 4 == 0) && (stride % 4 == 0) && ((col_q + h * d) % 4 == 0) &&
+                       ((col_k + h * d) % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  const bool wide_v = wide_qk && (n_cols % 4 == 0) && (cols_per_cta % 4 == 0) &&
+                      ((col_v + h * dv + j0) % 4 == 0);
   auto issue = [&](int t0, float* buf) {
     const int nt = min(LA_CHUNK, n_q - t0);
     float* q_s = buf;
     float* k_s = q_s + LA_CHUNK * DS;
     float* v_s = k_s + LA_CHUNK * DS;
-    for (int e = tid; e < nt * d; e += n_threads) {
-      const int t = e / d, i = e - t * d;
-      const float* row = src + (size_t)(row0 + t0 + t) * stride;
-      la_copy4(q_s + t * DS + i, row + col_q + h * d + i);
-      la_copy4(k_s + t * DS + i, row + col_k + h * d + i);
+    if (wide_qk) {
+      const int d4 = d >> 2;
+      for (int e = tid; e < nt * d4; e += n_threads) {
+        const int t = e / d4, i = (e - t * d4) * 4;
+        const float* row = src + (size_t)(row0 + t0 + t) * stride;
+        la_copy16(q_s + t * DS + i, row + col_q + h * d + i);
+        la_copy16(k_s + t * DS + i, row + col_k + h * d + i);
+      }
+    } else {
+      for (int e = tid; e < nt * d; e += n_threads) {
+        const int t = e / d, i = e - t * d;
+        const float* row = src + (size_t)(row0 + t0 + t) * stride;
+        la_copy4(q_s + t * DS + i, row + col_q + h * d + i);
+        la_copy4(k_s + t * DS + i, row + col_k + h * d + i);
+      }
     }
-    for (int e = tid; e < nt * n_cols; e += n_threads) {
-      const int t = e / n_cols, c = e - t * n_cols;
-      la_copy4(v_s + t * cols_per_cta + c, src + (size_t)(row0 + t0 + t) * stride + col_v + h * dv + j0 + c);
+    if (wide_v) {
+      const int c4 = n_cols >> 2;
+      for (int e = tid; e < nt * c4; e += n_threads) {
+        const int t = e / c4, c = (e - t * c4) * 4;
+        la_copy16(v_s + t * cols_per_cta + c, src + (size_t)(row0 + t0 + t) * stride + col_v + h * dv + j0 + c);
+      }
+    } else {
+      for (int e = tid; e < nt * n_cols; e += n_threads) {
+        const int t = e / n_cols, c = e - t * n_cols;
+        la_copy4(v_s + t * cols_per_cta + c, src + (size_t)(row0 + t0 + t) * stride + col_v + h * dv + j0 + c);
+      }
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
@@ -100,6 +128,7 @@ linear_attention_kernel(const float* src, int stride, int col_q, int col_k, int 
       }
     }
     __syncthreads();
+#pragma unroll 4
     for (int t = 0; t < nt; ++t) {
       const float v = live ? v_s[t * cols_per_cta + col_local] : 0.0f;
       const float4* qt = reinterpret_cast<const float4*>(q_s + t * DS + part * 4);
@@ -156,11 +185,12 @@ NB_EXPORT int nb_linear_attention(const float* src, int stride, int col_q, int c
     NB_CUDA(cudaGetDevice(&dev));
     NB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   }
-  // as many columns a CTA as 256 threads hold; fewer (down to a warp's worth) while the grid
-  // would not give every SM two CTAs
+  // as many columns a CTA as 256 threads hold (the CTAs of a head each stage and activate
+  // its queries and keys); fewer, down to a warp's worth, while the grid has fewer CTAs than
+  // the GPU has SMs
   int cols = 256 / lanes;
   if (cols > dv) cols = dv;
-  while (cols * lanes > 32 && (long long)((dv + cols - 1) / cols) * n_heads * n_seqs < 2LL * sms)
+  while (cols * lanes > 32 && (long long)((dv + cols - 1) / cols) * n_heads * n_seqs < (long long)sms)
     cols = (cols + 1) / 2;
   const int threads = ((cols * lanes + 31) / 32) * 32;
   const dim3 grid((dv + cols - 1) / cols, n_heads, n_seqs);

@@ -102,6 +102,7 @@ selective_scan_kernel(const float* x, const float* low, int low_stride, int col_
     __syncthreads();
     // (a warp's channels beyond the last one walk along on whatever the buffer holds: the
     // shuffles below want every lane, and nothing of theirs is written)
+#pragma unroll 4
     for (int t = 0; t < nt; ++t) {
       const float dt = dt_s[t * CH + cl], xv = x_s[t * CH + cl];
       const float dx = dt * xv;
