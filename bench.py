@@ -310,6 +310,7 @@ class OpTimer:
     def __init__(self, ops):
         import torch
         self.torch, self.ops, self.records, self._orig = torch, ops, [], {}
+        self._depth = 0
         # written before every timed call: it empties the L2 (larger than its 126 MB), and while
         # the GPU is busy with it the host gets the call's launches queued, so that the events
         # see the kernels' time and not the host's
@@ -327,10 +328,16 @@ class OpTimer:
         torch = self.torch
 
         def call(*a, **kw):
+            if self._depth:      # an op that hands on to another one is timed once, as itself
+                return fn(*a, **kw)
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             self.flush.zero_()
             t0.record()
-            fn(*a, **kw)
+            self._depth += 1
+            try:
+                fn(*a, **kw)
+            finally:
+                self._depth -= 1
             t1.record()
             self.records.append((kind, self._label(kind, a, kw), t0, t1, *self._work(kind, a, kw)))
         return call

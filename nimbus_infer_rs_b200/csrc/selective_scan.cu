@@ -94,10 +94,14 @@ selective_scan_kernel(const float* x, const float* low, int low_stride, int col_
     float* bc_s = buf;
     float* dt_s = buf + SS_CHUNK * 2 * N;
     const float* x_s = dt_s + SS_CHUNK * CH;
-    const float* z_s = x_s + SS_CHUNK * CH;
+    float* z_s = dt_s + 2 * SS_CHUNK * CH;
+    // step sizes and gates once per (token, channel), by all threads, ahead of the walk
     for (int i = tid; i < nt * CH; i += SS_THREADS) {
       const int k = i % CH;
-      if (k < n_ch) dt_s[i] = ss_softplus(dt_s[i] + dt_bias[c0 + k]);
+      if (k < n_ch) {
+        dt_s[i] = ss_softplus(dt_s[i] + dt_bias[c0 + k]);
+        z_s[i] = nb_silu(z_s[i]);
+      }
     }
     __syncthreads();
     // (a warp's channels beyond the last one walk along on whatever the buffer holds: the
@@ -125,7 +129,7 @@ selective_scan_kernel(const float* x, const float* low, int low_stride, int col_
       for (int m = LANES / 2; m > 0; m >>= 1) y += __shfl_xor_sync(0xffffffffu, y, m);
       if (part == 0 && live) {
         y = fmaf(dsk, xv, y);
-        out[(size_t)(row0 + t0 + t) * inner + c] = nb_from_f32<TOut>(y * nb_silu(z_s[t * CH + cl]));
+        out[(size_t)(row0 + t0 + t) * inner + c] = nb_from_f32<TOut>(y * z_s[t * CH + cl]);
       }
     }
   }

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from ..csrc.ops import ACT_SILU
+from ..csrc.ops import ACT_NONE, ACT_SILU
 from .base import VECTOR, Mixer, ParamSpec, StateRequest, register_part
 from .linear import Linear
 
@@ -60,8 +60,12 @@ class DecayedLinearAttention(Mixer):
         lay, ops = ctx.layout, ctx.ops
         n, dev = lay.n_rows, h.device
         fused = self.proj(ctx, h, out_dtype=torch.float32)
+        # the activation once per number, ahead of the recurrence: there every CTA of a head
+        # stages the head's queries and keys, and would activate them again
+        qkv = torch.empty((n, self.col_g), device=dev, dtype=torch.float32)
+        ops.act_rows(fused, 0, ACT_SILU, None, qkv)
         o = torch.empty((n, self.v_width), device=dev, dtype=torch.float32)
-        ops.linear_attention(fused, self.col_q, self.col_k, self.col_v, ACT_SILU, self.decay,
+        ops.linear_attention(qkv, self.col_q, self.col_k, self.col_v, ACT_NONE, self.decay,
                              ctx.state, lay, self.n_heads, self.head_dim, self.value_dim, o)
         y = torch.empty((n, self.v_width), device=dev, dtype=ctx.rt.act_dtype)
         ops.rmsnorm_gated(o, self.norm, fused, self.col_g, self.eps, y)
