@@ -40,8 +40,10 @@ selective_scan_kernel(const float* x, const float* low, int low_stride, int col_
   nb_grid_dependency_wait();
   nb_launch_dependents();
   constexpr int CH = SS_THREADS / LANES;               // channels of a CTA
-  extern __shared__ float ss_smem[];
-  const int buf_floats = SS_CHUNK * (2 * N + 3 * CH);  // [CHUNK][2N] B|C, then dt, x, z [CHUNK][CH]
+  constexpr int NP = NPER * LANES;                     // a staged row of B or C, N and zeros
+  static_assert(NPER % 4 == 0, "a lane reads its part of B and C as 16-byte pieces");
+  extern __shared__ __align__(16) float ss_smem[];
+  const int buf_floats = SS_CHUNK * (2 * NP + 3 * CH); // [CHUNK][2NP] B|C, then dt, x, z [CHUNK][CH]
   const int s = blockIdx.y;
   const int slot = seq_slot[s];
   const int row0 = cu_rows[s], n_q = cu_rows[s + 1] - row0;
@@ -61,16 +63,22 @@ selective_scan_kernel(const float* x, const float* low, int low_stride, int col_
     A[a] = has ? -expf(a_log[(size_t)c * N + n0 + a]) : 0.0f;
   }
   const float dsk = live ? d_skip[c] : 0.0f;
+  // the rows of B and C beyond N stay zero, so the walk below needs no bounds (a state number
+  // beyond N has A = 0 and stays 0)
+  for (int i = tid; i < 2 * buf_floats; i += SS_THREADS) ss_smem[i] = 0.0f;
+  __syncthreads();
 
   auto issue = [&](int t0, float* buf) {
     const int nt = min(SS_CHUNK, n_q - t0);
     float* bc_s = buf;
-    float* dt_s = buf + SS_CHUNK * 2 * N;
+    float* dt_s = buf + SS_CHUNK * 2 * NP;
     float* x_s = dt_s + SS_CHUNK * CH;
     float* z_s = x_s + SS_CHUNK * CH;
     for (int i = tid; i < nt * 2 * N; i += SS_THREADS) {
       const int t = i / (2 * N), j = i - t * 2 * N;
-      ss_copy4(bc_s + i, low + (size_t)(row0 + t0 + t) * low_stride + (j < N ? col_b + j : col_c + j - N));
+      const float* row = low + (size_t)(row0 + t0 + t) * low_stride;
+      if (j < N) ss_copy4(bc_s + t * 2 * NP + j, row + col_b + j);
+      else ss_copy4(bc_s + t * 2 * NP + NP + j - N, row + col_c + j - N);
     }
     for (int i = tid; i < nt * CH; i += SS_THREADS) {
       const int t = i / CH, k = i - t * CH;
@@ -92,7 +100,7 @@ selective_scan_kernel(const float* x, const float* low, int low_stride, int col_
     __syncthreads();     // the chunk is in; everyone is done with the other buffer
     if (t0 + SS_CHUNK < n_q) issue(t0 + SS_CHUNK, ss_smem + (which ^ 1) * buf_floats);
     float* bc_s = buf;
-    float* dt_s = buf + SS_CHUNK * 2 * N;
+    float* dt_s = buf + SS_CHUNK * 2 * NP;
     const float* x_s = dt_s + SS_CHUNK * CH;
     float* z_s = dt_s + 2 * SS_CHUNK * CH;
     // step sizes and gates once per (token, channel), by all threads, ahead of the walk
@@ -110,19 +118,20 @@ selective_scan_kernel(const float* x, const float* low, int low_stride, int col_
     for (int t = 0; t < nt; ++t) {
       const float dt = dt_s[t * CH + cl], xv = x_s[t * CH + cl];
       const float dx = dt * xv;
-      const float* B = bc_s + t * 2 * N + n0;
-      const float* Cv = B + N;
+      const float4* B4 = reinterpret_cast<const float4*>(bc_s + t * 2 * NP + n0);
+      const float4* C4 = B4 + NP / 4;
       float y0 = 0.0f, y1 = 0.0f;
 #pragma unroll
-      for (int a = 0; a < NPER; a += 2) {
-        if (n0 + a < N) {
-          S[a] = fmaf(expf(dt * A[a]), S[a], dx * B[a]);
-          y0 = fmaf(S[a], Cv[a], y0);
-        }
-        if (a + 1 < NPER && n0 + a + 1 < N) {
-          S[a + 1] = fmaf(expf(dt * A[a + 1]), S[a + 1], dx * B[a + 1]);
-          y1 = fmaf(S[a + 1], Cv[a + 1], y1);
-        }
+      for (int g = 0; g < NPER / 4; ++g) {
+        const float4 b = B4[g], cv = C4[g];
+        S[4 * g] = fmaf(expf(dt * A[4 * g]), S[4 * g], dx * b.x);
+        y0 = fmaf(S[4 * g], cv.x, y0);
+        S[4 * g + 1] = fmaf(expf(dt * A[4 * g + 1]), S[4 * g + 1], dx * b.y);
+        y1 = fmaf(S[4 * g + 1], cv.y, y1);
+        S[4 * g + 2] = fmaf(expf(dt * A[4 * g + 2]), S[4 * g + 2], dx * b.z);
+        y0 = fmaf(S[4 * g + 2], cv.z, y0);
+        S[4 * g + 3] = fmaf(expf(dt * A[4 * g + 3]), S[4 * g + 3], dx * b.w);
+        y1 = fmaf(S[4 * g + 3], cv.w, y1);
       }
       float y = y0 + y1;
 #pragma unroll
@@ -147,7 +156,7 @@ int launch_scan(const float* x, const float* low, int low_stride, int col_b, int
                 int n_seqs, cudaStream_t stream) {
   constexpr int CH = SS_THREADS / LANES;
   const dim3 grid((inner + CH - 1) / CH, n_seqs);
-  const size_t smem = (size_t)2 * SS_CHUNK * (2 * N + 3 * CH) * sizeof(float);
+  const size_t smem = (size_t)2 * SS_CHUNK * (2 * NPER * LANES + 3 * CH) * sizeof(float);
   if (out_dtype == NB_F32) {
     auto kern = selective_scan_kernel<NPER, LANES, float>;
     if (smem > 48 * 1024)
