@@ -25,7 +25,8 @@ namespace {
 
 constexpr int CV_THREADS = 128;
 constexpr int CV_MAX_TAPS = 16;
-constexpr int CV_TOKENS = 8;       // tokens a CTA walks in a step of more than one token per sequence
+constexpr int CV_TILE_W = CV_THREADS + 1;   // a staged row: the CTA's channels and the one after
+constexpr int CV_TOKENS = 16;      // tokens a CTA walks in a step of more than one token per sequence
 
 // the convolution's result for channel c of the sequence's token t (row = row0 + t)
 __device__ __forceinline__ float conv_at(const float* src, int stride, int col0, int row0, int t,
@@ -71,13 +72,81 @@ __device__ __forceinline__ float conv_step(float x, int c, const float* __restri
   return fmaf(W[(size_t)c * taps + taps - 1], x, y);
 }
 
-// A CTA takes CV_THREADS consecutive channels (blockIdx.z) of CV_TOKENS consecutive tokens
-// (blockIdx.x) of a sequence (blockIdx.y); a thread keeps its channel and walks the tokens, so
-// that the taps' inputs of the next token are the ones it has just read (they come from L1).
+// A CTA first stages the inputs of its channels for its run of tokens, and the taps - 1 inputs
+// before the run (from earlier rows of the step or from the state row), in shared memory: every
+// thread fetches its own channel's column, all fetches in flight together (a thread that walked
+// the tokens with one fetch at a time kept too few bytes in flight to use the memory's
+// bandwidth).  Row r of the tile is token t_begin - (taps - 1) + r.
+template <int MT>
+__device__ __forceinline__ void conv_stage(float* tile, const float* src, int stride, int col0,
+                                           int row0, int t_begin, int t_end, int c, int taps,
+                                           const float* state_row, int n_channels,
+                                           bool one_more) {
+  const int before = taps > 1 ? taps - 1 : 0;
+  const int rows = before + t_end - t_begin;
+  if (c < n_channels) {
+#pragma unroll 8
+    for (int r = 0; r < rows; ++r) {
+      const int tt = t_begin - before + r;
+      tile[r * CV_TILE_W + threadIdx.x] =
+          tt >= 0 ? src[(size_t)(row0 + tt) * stride + col0 + c]
+                  : state_row[(size_t)(before + tt) * n_channels + c];
+    }
+  }
+  // the channel after the CTA's last one: the partner of a rotated pair that starts there
+  if (one_more && threadIdx.x == CV_THREADS - 1 && c + 1 < n_channels)
+    for (int r = 0; r < rows; ++r) {
+      const int tt = t_begin - before + r;
+      tile[r * CV_TILE_W + CV_THREADS] =
+          tt >= 0 ? src[(size_t)(row0 + tt) * stride + col0 + c + 1]
+                  : state_row[(size_t)(before + tt) * n_channels + c + 1];
+    }
+}
+
+// A channel's walk over the staged run: its weights and the taps' inputs before the next token
+// stay in registers (MT slots, the newest tap in the last one, so that every index is known to
+// the compiler; taps <= MT).  The products are added oldest tap first, as conv_at and conv_step
+// add them: a token's number does not depend on which of the three computed it.
+template <int MT>
+struct ConvWalk {
+  float w[MT], h[MT - 1];
+  const float* col;     // the channel's column of the tile, at the run's first token
+  int taps;
+  __device__ __forceinline__ void start(const float* tile_col, int c, const float* __restrict__ W,
+                                        int taps_) {
+    taps = taps_;
+    const int before = taps > 1 ? taps - 1 : 0;
+    col = tile_col + before * CV_TILE_W;
+#pragma unroll
+    for (int k = 0; k < MT; ++k) {
+      const int j = k - (MT - taps);                       // tap j sits in slot k
+      w[k] = j >= 0 ? W[(size_t)c * taps + j] : 0.0f;
+      if (k < MT - 1) h[k] = j >= 0 ? tile_col[j * CV_TILE_W] : 0.0f;
+    }
+  }
+  // the convolution at token number u of the run
+  __device__ __forceinline__ float next(int u) {
+    const float x = col[u * CV_TILE_W];
+    if (taps <= 0) return x;
+    float y = 0.0f;
+#pragma unroll
+    for (int k = 0; k < MT - 1; ++k) {
+      if (k >= MT - taps) y = fmaf(w[k], h[k], y);
+      if (k < MT - 2) h[k] = h[k + 1];
+    }
+    if (MT > 1) h[MT - 2] = x;
+    return fmaf(w[MT - 1], x, y);
+  }
+};
+
+// A CTA takes CV_THREADS consecutive channels (blockIdx.x) of CV_TOKENS consecutive tokens
+// (blockIdx.z) of a sequence (blockIdx.y): the CTAs that run side by side read neighbouring
+// pieces of the same rows.  A thread keeps its channel and walks the tokens with a ConvWalk (a
+// step of one token per sequence reads and moves the state row instead).
 // Of a rotated pair the thread of the even number does both (it needs both convolutions
 // anyway) and the other one rests: every channel is then read, and its state row written, by
 // one thread only.
-template <typename TQ, typename TC>
+template <typename TQ, typename TC, int MT>
 __global__ void __launch_bounds__(CV_THREADS)
 conv_rope_append_kernel(const float* src, int stride, int col0, const float* __restrict__ W,
                         int taps, float* state, int state_stride, const int* cu_rows,
@@ -87,21 +156,26 @@ conv_rope_append_kernel(const float* src, int stride, int col0, const float* __r
                         int n_kv_heads, int d, int dv, int tokens_per_cta, int fused_update) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
-  const int s = blockIdx.y, t_begin = blockIdx.x * tokens_per_cta;
+  const int s = blockIdx.y, t_begin = blockIdx.z * tokens_per_cta;
   const int row0 = cu_rows[s], n_q = cu_rows[s + 1] - row0;
   if (t_begin >= n_q) return;
   const int t_end = min(n_q, t_begin + tokens_per_cta);
   const int slot = seq_slot[s];
   const int qw = n_heads * d, kw = n_kv_heads * d, vw = n_kv_heads * dv;
   const int C = qw + kw + vw;
-  const int c = blockIdx.z * CV_THREADS + threadIdx.x;
-  if (c >= C) return;
+  const int c = blockIdx.x * CV_THREADS + threadIdx.x;
   if (slot < 0) {
     if (c < qw)
       for (int t = t_begin; t < t_end; ++t) q_out[(size_t)(row0 + t) * qw + c] = nb_from_f32<TQ>(0.0f);
     return;
   }
   float* st = state + (size_t)slot * state_stride;
+  __shared__ float tile[(CV_TOKENS + MT - 1) * CV_TILE_W];
+  if (!fused_update) {
+    conv_stage<MT>(tile, src, stride, col0, row0, t_begin, t_end, c, taps, st, C, rot_dims > 0);
+    __syncthreads();
+  }
+  if (c >= C) return;
   // where the channel goes: a value; or number i of a query or key head
   const bool is_v = c >= qw + kw, is_q = c < qw;
   const int e = is_v ? c - qw - kw : (is_q ? c : c - qw);
@@ -109,20 +183,34 @@ conv_rope_append_kernel(const float* src, int stride, int col0, const float* __r
   const bool turned = !is_v && i < rot_dims;
   if (turned && (i & 1)) return;               // its partner does both
   const float f = turned ? freq[i >> 1] : 0.0f;
-  for (int t = t_begin; t < t_end; ++t) {
+  ConvWalk<MT> walk, walk2;
+  if (!fused_update) {
+    walk.start(tile + threadIdx.x, c, W, taps);
+    if (turned) walk2.start(tile + threadIdx.x + 1, c + 1, W, taps);
+  }
+  // the cache row of the token: its page from the table when the walk enters one
+  const int pos_begin = seq_pos0[s] + t_begin;
+  int pg = pos_begin / page, off = pos_begin - pg * page;
+  const int* table = is_v ? v_table + (size_t)slot * v_max_pages : k_table + (size_t)slot * k_max_pages;
+  size_t page_row = is_q ? 0 : (size_t)table[pg] * n_kv_heads * page;
+  for (int t = t_begin; t < t_end; ++t, ++off) {
     const int pos = seq_pos0[s] + t;
+    if (off == page) {
+      off = 0;
+      ++pg;
+      if (!is_q) page_row = (size_t)table[pg] * n_kv_heads * page;
+    }
     float y, y2 = 0.0f;
     if (fused_update) {
       const float* row = src + (size_t)(row0 + t) * stride + col0;
       y = conv_step(row[c], c, W, taps, st, C);
       if (turned) y2 = conv_step(row[c + 1], c + 1, W, taps, st, C);
     } else {
-      y = conv_at(src, stride, col0, row0, t, c, W, taps, st, C);
-      if (turned) y2 = conv_at(src, stride, col0, row0, t, c + 1, W, taps, st, C);
+      y = walk.next(t - t_begin);
+      if (turned) y2 = walk2.next(t - t_begin);
     }
     if (is_v) {
-      const size_t v_row = (size_t)v_table[(size_t)slot * v_max_pages + pos / page] * n_kv_heads * page + (pos % page);
-      vc[(v_row + (size_t)hh * page) * dv + i] = nb_from_f32<TC>(y);
+      vc[(page_row + off + (size_t)hh * page) * dv + i] = nb_from_f32<TC>(y);
       continue;
     }
     if (turned) {
@@ -137,15 +225,14 @@ conv_rope_append_kernel(const float* src, int stride, int col0, const float* __r
       qo[0] = nb_from_f32<TQ>(y);
       if (turned) qo[1] = nb_from_f32<TQ>(y2);
     } else {
-      const size_t k_row = (size_t)k_table[(size_t)slot * k_max_pages + pos / page] * n_kv_heads * page + (pos % page);
-      TC* ko = kc + (k_row + (size_t)hh * page) * d + i;
+      TC* ko = kc + (page_row + off + (size_t)hh * page) * d + i;
       ko[0] = nb_from_f32<TC>(y);
       if (turned) ko[1] = nb_from_f32<TC>(y2);
     }
   }
 }
 
-template <typename TOut>
+template <typename TOut, int MT>
 __global__ void __launch_bounds__(CV_THREADS)
 conv_act_kernel(const float* src, int stride, int col0, const float* __restrict__ W,
                 const float* __restrict__ bias, int taps, int act, float* state, int state_stride,
@@ -153,25 +240,33 @@ conv_act_kernel(const float* src, int stride, int col0, const float* __restrict_
                 int tokens_per_cta, int fused_update) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
-  const int s = blockIdx.y, t_begin = blockIdx.x * tokens_per_cta;
+  const int s = blockIdx.y, t_begin = blockIdx.z * tokens_per_cta;
   const int row0 = cu_rows[s], n_q = cu_rows[s + 1] - row0;
   if (t_begin >= n_q) return;
   const int t_end = min(n_q, t_begin + tokens_per_cta);
   const int slot = seq_slot[s];
-  const int c = blockIdx.z * CV_THREADS + threadIdx.x;
-  if (c >= C) return;
+  const int c = blockIdx.x * CV_THREADS + threadIdx.x;
   if (slot < 0) {
-    for (int t = t_begin; t < t_end; ++t) {
-      out_f32[(size_t)(row0 + t) * C + c] = 0.0f;
-      if (out_act != nullptr) out_act[(size_t)(row0 + t) * C + c] = nb_from_f32<TOut>(0.0f);
-    }
+    if (c < C)
+      for (int t = t_begin; t < t_end; ++t) {
+        out_f32[(size_t)(row0 + t) * C + c] = 0.0f;
+        if (out_act != nullptr) out_act[(size_t)(row0 + t) * C + c] = nb_from_f32<TOut>(0.0f);
+      }
     return;
   }
   float* st = state + (size_t)slot * state_stride;
+  __shared__ float tile[(CV_TOKENS + MT - 1) * CV_TILE_W];
+  if (!fused_update) {
+    conv_stage<MT>(tile, src, stride, col0, row0, t_begin, t_end, c, taps, st, C, false);
+    __syncthreads();
+  }
+  if (c >= C) return;
   const float b = bias != nullptr ? bias[c] : 0.0f;
+  ConvWalk<MT> walk;
+  if (!fused_update) walk.start(tile + threadIdx.x, c, W, taps);
   for (int t = t_begin; t < t_end; ++t) {
     float y = fused_update ? conv_step(src[(size_t)(row0 + t) * stride + col0 + c], c, W, taps, st, C)
-                           : conv_at(src, stride, col0, row0, t, c, W, taps, st, C);
+                           : walk.next(t - t_begin);
     y = nb_apply_act(y + b, act);
     out_f32[(size_t)(row0 + t) * C + c] = y;
     if (out_act != nullptr) out_act[(size_t)(row0 + t) * C + c] = nb_from_f32<TOut>(y);
@@ -222,13 +317,18 @@ NB_EXPORT int nb_conv_rope_append(const float* src, int stride, int col0, const 
              "conv_rope_append: the state is updated in place only in steps of one token");
   const int channels = n_heads * d + n_kv_heads * (d + dv);
   const int per_cta = max_q_len == 1 ? 1 : CV_TOKENS;
-  const dim3 grid((max_q_len + per_cta - 1) / per_cta, n_seqs, (channels + CV_THREADS - 1) / CV_THREADS);
-  NB_REQUIRE(grid.z <= 65535, NB_ERR_UNSUPPORTED, "conv_rope_append: %d channels", channels);
-#define NB_CRA(TQ, TC)                                                                            \
-  NB_CUDA(nb_launch(conv_rope_append_kernel<TQ, TC>, grid, dim3(CV_THREADS), 0, stream, src,      \
+  const dim3 grid((channels + CV_THREADS - 1) / CV_THREADS, n_seqs, (max_q_len + per_cta - 1) / per_cta);
+  NB_REQUIRE(grid.z <= 65535, NB_ERR_UNSUPPORTED, "conv_rope_append: a step of %d tokens", max_q_len);
+#define NB_CRA_MT(TQ, TC, MT)                                                                     \
+  NB_CUDA(nb_launch(conv_rope_append_kernel<TQ, TC, MT>, grid, dim3(CV_THREADS), 0, stream, src,  \
                     stride, col0, W, taps, state, state_stride, cu_rows, seq_slot, seq_pos0, freq, \
                     rot_dims, (TQ*)q_out, (TC*)kc, k_table, k_max_pages, (TC*)vc, v_table,        \
                     v_max_pages, page, n_heads, n_kv_heads, d, dv, per_cta, fused_update))
+#define NB_CRA(TQ, TC)                                                                            \
+  do {                                                                                            \
+    if (taps <= 4) NB_CRA_MT(TQ, TC, 4);                                                          \
+    else NB_CRA_MT(TQ, TC, CV_MAX_TAPS);                                                          \
+  } while (0)
   switch (q_dtype * 2 + cache_dtype) {
     case 0: NB_CRA(float, float); break;
     case 1: NB_CRA(float, bf16); break;
@@ -237,6 +337,7 @@ NB_EXPORT int nb_conv_rope_append(const float* src, int stride, int col0, const 
     default: NB_REQUIRE(false, NB_ERR_BAD_ARG, "conv_rope_append: unknown dtypes %d/%d", q_dtype, cache_dtype);
   }
 #undef NB_CRA
+#undef NB_CRA_MT
   NB_CHECK_LAUNCH("conv_rope_append");
   return 0;
 }
@@ -255,18 +356,22 @@ NB_EXPORT int nb_conv_act(const float* src, int stride, int col0, const float* W
   NB_REQUIRE(!fused_update || max_q_len == 1, NB_ERR_BAD_ARG,
              "conv_act: the state is updated in place only in steps of one token");
   const int per_cta = max_q_len == 1 ? 1 : CV_TOKENS;
-  const dim3 grid((max_q_len + per_cta - 1) / per_cta, n_seqs, (n_channels + CV_THREADS - 1) / CV_THREADS);
-  NB_REQUIRE(grid.z <= 65535, NB_ERR_UNSUPPORTED, "conv_act: %d channels", n_channels);
-  if (out_act == nullptr || act_dtype == NB_F32)
-    NB_CUDA(nb_launch(conv_act_kernel<float>, grid, dim3(CV_THREADS), 0, stream, src, stride, col0,
-                      W, bias, taps, act, state, state_stride, cu_rows, seq_slot, n_channels,
-                      out_f32, (float*)out_act, per_cta, fused_update));
-  else if (act_dtype == NB_BF16)
-    NB_CUDA(nb_launch(conv_act_kernel<bf16>, grid, dim3(CV_THREADS), 0, stream, src, stride, col0,
-                      W, bias, taps, act, state, state_stride, cu_rows, seq_slot, n_channels,
-                      out_f32, (bf16*)out_act, per_cta, fused_update));
-  else
+  const dim3 grid((n_channels + CV_THREADS - 1) / CV_THREADS, n_seqs, (max_q_len + per_cta - 1) / per_cta);
+  NB_REQUIRE(grid.z <= 65535, NB_ERR_UNSUPPORTED, "conv_act: a step of %d tokens", max_q_len);
+#define NB_CA(T, MT)                                                                              \
+  NB_CUDA(nb_launch(conv_act_kernel<T, MT>, grid, dim3(CV_THREADS), 0, stream, src, stride, col0, \
+                    W, bias, taps, act, state, state_stride, cu_rows, seq_slot, n_channels,       \
+                    out_f32, (T*)out_act, per_cta, fused_update))
+  if (out_act == nullptr || act_dtype == NB_F32) {
+    if (taps <= 4) NB_CA(float, 4);
+    else NB_CA(float, CV_MAX_TAPS);
+  } else if (act_dtype == NB_BF16) {
+    if (taps <= 4) NB_CA(bf16, 4);
+    else NB_CA(bf16, CV_MAX_TAPS);
+  } else {
     NB_REQUIRE(false, NB_ERR_BAD_ARG, "conv_act: unknown dtype %d", act_dtype);
+  }
+#undef NB_CA
   NB_CHECK_LAUNCH("conv_act");
   return 0;
 }
