@@ -143,9 +143,6 @@ struct ConvWalk {
 // (blockIdx.z) of a sequence (blockIdx.y): the CTAs that run side by side read neighbouring
 // pieces of the same rows.  A thread keeps its channel and walks the tokens with a ConvWalk (a
 // step of one token per sequence reads and moves the state row instead).
-// Of a rotated pair the thread of the even number does both (it needs both convolutions
-// anyway) and the other one rests: every channel is then read, and its state row written, by
-// one thread only.
 template <typename TQ, typename TC, int MT>
 __global__ void __launch_bounds__(CV_THREADS)
 conv_rope_append_kernel(const float* src, int stride, int col0, const float* __restrict__ W,
@@ -178,22 +175,40 @@ conv_rope_append_kernel(const float* src, int stride, int col0, const float* __r
   if (c >= C) return;
   // where the channel goes: a value; or number i of a query or key head
   const bool is_v = c >= qw + kw, is_q = c < qw;
-  const int e = is_v ? c - qw - kw : (is_q ? c : c - qw);
-  const int hh = e / (is_v ? dv : d), i = e - hh * (is_v ? dv : d);
-  const bool turned = !is_v && i < rot_dims;
-  if (turned && (i & 1)) return;               // its partner does both
+  const int e0 = is_v ? c - qw - kw : (is_q ? c : c - qw);
+  const int hh = e0 / (is_v ? dv : d), i0 = e0 - hh * (is_v ? dv : d);
+  const bool turned = !is_v && i0 < rot_dims;
+  // A rotated pair needs both convolutions for either number, so one thread does both numbers
+  // of a token; the pair's two threads share the run's tokens, the first half to the even one
+  // (all of them where the partner sits in another CTA, and in a step of one token, where a
+  // channel's state row has one owner).
+  const bool odd = turned && (i0 & 1);
+  int u_lo = 0, u_hi = t_end - t_begin;
+  if (turned) {
+    const bool partner_here = odd ? threadIdx.x > 0 : threadIdx.x < CV_THREADS - 1;
+    if (!partner_here || fused_update) {
+      if (odd) return;
+    } else {
+      const int half = (u_hi + 1) / 2;
+      if (odd) u_lo = half;
+      else u_hi = half;
+    }
+  }
+  if (u_lo >= u_hi) return;
+  const int pc = c - (odd ? 1 : 0), ptid = (int)threadIdx.x - (odd ? 1 : 0);   // the pair's even channel
+  const int e = e0 - (odd ? 1 : 0), i = i0 - (odd ? 1 : 0);
   const float f = turned ? freq[i >> 1] : 0.0f;
   ConvWalk<MT> walk, walk2;
   if (!fused_update) {
-    walk.start(tile + threadIdx.x, c, W, taps);
-    if (turned) walk2.start(tile + threadIdx.x + 1, c + 1, W, taps);
+    walk.start(tile + u_lo * CV_TILE_W + ptid, pc, W, taps);
+    if (turned) walk2.start(tile + u_lo * CV_TILE_W + ptid + 1, pc + 1, W, taps);
   }
   // the cache row of the token: its page from the table when the walk enters one
-  const int pos_begin = seq_pos0[s] + t_begin;
+  const int pos_begin = seq_pos0[s] + t_begin + u_lo;
   int pg = pos_begin / page, off = pos_begin - pg * page;
   const int* table = is_v ? v_table + (size_t)slot * v_max_pages : k_table + (size_t)slot * k_max_pages;
   size_t page_row = is_q ? 0 : (size_t)table[pg] * n_kv_heads * page;
-  for (int t = t_begin; t < t_end; ++t, ++off) {
+  for (int t = t_begin + u_lo; t < t_begin + u_hi; ++t, ++off) {
     const int pos = seq_pos0[s] + t;
     if (off == page) {
       off = 0;
@@ -203,11 +218,11 @@ conv_rope_append_kernel(const float* src, int stride, int col0, const float* __r
     float y, y2 = 0.0f;
     if (fused_update) {
       const float* row = src + (size_t)(row0 + t) * stride + col0;
-      y = conv_step(row[c], c, W, taps, st, C);
-      if (turned) y2 = conv_step(row[c + 1], c + 1, W, taps, st, C);
+      y = conv_step(row[pc], pc, W, taps, st, C);
+      if (turned) y2 = conv_step(row[pc + 1], pc + 1, W, taps, st, C);
     } else {
-      y = walk.next(t - t_begin);
-      if (turned) y2 = walk2.next(t - t_begin);
+      y = walk.next(t - t_begin - u_lo);
+      if (turned) y2 = walk2.next(t - t_begin - u_lo);
     }
     if (is_v) {
       vc[(page_row + off + (size_t)hh * page) * dv + i] = nb_from_f32<TC>(y);
