@@ -154,6 +154,9 @@ def _plain_attention(q, k, v, conv, rot, scale, softcap, sink):
     dict(H=2, G=1, d=3, dv=1, taps=0, cap=2.0, rot=dict(dims=2, base=10.0)),
     dict(H=4, G=1, d=64, dv=64, taps=4, cap=0.0, scale=0.04, rot=dict(dims=64, base=1e4)),
     dict(H=2, G=2, d=33, dv=130, taps=7, cap=50.0, rot=dict(dims=32, base=500.0, scaling=dict(factor=4.0, low=1.0, high=4.0, original=64))),
+    # an odd head size: the second head's rotated pairs start at odd channels, and one of them
+    # lies across the border between two blocks of 128 channels
+    dict(H=2, G=1, d=85, dv=9, taps=3, cap=9.0, scale=0.1, rot=dict(dims=84, base=200.0)),
     # head sizes that the tensor-core prompt kernel and the decode kernel of plain attention take
     dict(H=6, G=2, d=64, dv=64, taps=3, cap=4.0, scale=0.09, rot=dict(dims=32, base=300.0)),
     dict(H=4, G=4, d=128, dv=128, taps=2, cap=12.0, scale=0.05, rot=dict(dims=128, base=1e4)),
