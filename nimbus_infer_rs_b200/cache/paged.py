@@ -13,7 +13,8 @@ once, so a sequence's block table (its list of pages) is shared by the group's l
 
 A group with a window gives a page back to its pool as soon as every token of the page lies
 before the window of the sequence's next token (``trim``): a long sequence then holds about
-``window / PAGE + 2`` pages of that group, while a group without a window holds them all.
+``window / PAGE + 2`` pages of that group (plus the pages of the first ``keep_first`` tokens, if
+the request keeps them visible), while a group without a window holds them all.
 The block-table entry of a page that was given back is never read again (the kernels start at
 the window's first key), so it is left as it is.
 
@@ -129,10 +130,12 @@ class CacheGroup:
         if w <= 0 or not pages:
             return 0
         first_needed = max(0, length - w + 1) // PAGE
-        gone = [p for p in pages[:first_needed] if p >= 0]
+        # the pages of the kept first tokens stay with the sequence
+        kept = min(pages_for(self.request.keep_first), first_needed)
+        gone = [p for p in pages[kept:first_needed] if p >= 0]
         if gone:
             self.pool.release(gone)
-            pages[:first_needed] = [-1] * first_needed
+            pages[kept:first_needed] = [-1] * (first_needed - kept)
         return len(gone)
 
     def release(self, slot: int) -> None:

@@ -3,12 +3,13 @@ from .gpt2 import ACT_ERF, ACT_TANH, GPT2Config
 from .runesun import RunesunConfig
 from .rizitar import RizitarConfig
 from .pinozen import PinozenConfig
+from .lulizen import LulizenConfig
 from .presets import load_preset, preset_json, preset_names, preset_random_options
 from .registry import (Architecture, architectures, get_architecture, load_config,
                        register_architecture, resolve_architecture)
 
 __all__ = [
-    "ConfigError", "Field", "load_json", "read_fields", "GPT2Config", "RunesunConfig", "RizitarConfig", "PinozenConfig", "ACT_TANH", "ACT_ERF",
+    "ConfigError", "Field", "load_json", "read_fields", "GPT2Config", "RunesunConfig", "RizitarConfig", "PinozenConfig", "LulizenConfig", "ACT_TANH", "ACT_ERF",
     "Architecture", "architectures", "get_architecture", "load_config",
     "register_architecture", "resolve_architecture", "load_preset", "preset_json",
     "preset_names", "preset_random_options",

@@ -5,6 +5,13 @@
 //   weights = softmax over the seen keys, the denominator holding one more term exp(sink_h)
 //             (no key, no value; neither scaled nor capped)
 //
+// What a position sees (nb_attention_masked; nb_attention_capped sees every j <= i):
+//   window > 0:  j <= i with i - j < window, and also every j < keep_first (the first tokens
+//                stay visible, at their true positions)
+//   chunk > 0:   j <= i with floor(i / chunk) == floor(j / chunk), chunks counted from position 0
+// With `gate` (fp32 rows, one logit per head at columns gate_col ..) head h's result is
+// multiplied by sigmoid(gate[r][gate_col + h]).
+//
 // fp32 arithmetic on the CUDA cores, any sizes, bf16 or fp32 storage: the 32-bit path, and the
 // path of shapes the tensor-core kernel leaves out.  A CTA per (row, head); the scores of up to
 // 1024 keys at a time in shared memory; warps over keys, lanes over the head's numbers; every
@@ -24,7 +31,9 @@ __global__ void __launch_bounds__(AC_THREADS)
 attention_capped_kernel(const TQ* q, const int* row_slot, const int* row_pos, const TC* kc,
                         const int* k_table, int k_max_pages, const TC* vc, const int* v_table,
                         int v_max_pages, int page, int n_heads, int n_kv_heads, int d, int dv,
-                        const float* __restrict__ sink, TOut* out, float scale, float softcap) {
+                        const float* __restrict__ sink, TOut* out, float scale, float softcap,
+                        int window, int keep_first, int chunk, const float* gate, int gate_stride,
+                        int gate_col) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
   __shared__ float scores[AC_CHUNK];
@@ -46,7 +55,14 @@ attention_capped_kernel(const TQ* q, const int* row_slot, const int* row_pos, co
   const TQ* qr = q + ((size_t)r * n_heads + h) * d;
   for (int i = tid; i < d; i += AC_THREADS) q_s[i] = nb_to_f32(qr[i]);
   __syncthreads();
-  const int n_seen = pos + 1;
+  // the seen keys: [0, n_head) and [lo, pos]; index t of the walk is key t below n_head, else
+  // key lo + (t - n_head)
+  int lo = 0;
+  if (chunk > 0) lo = (pos / chunk) * chunk;
+  if (window > 0) lo = max(lo, pos - window + 1);
+  const int n_head = window > 0 ? min(keep_first, lo) : 0;
+  const int shift = lo - n_head;
+  const int n_seen = n_head + pos + 1 - lo;
   float m_run = -INFINITY, l_run = 0.0f;
   float acc[AC_DPL];
 #pragma unroll
@@ -56,13 +72,14 @@ attention_capped_kernel(const TQ* q, const int* row_slot, const int* row_pos, co
   for (int c0 = 0; c0 < n_seen; c0 += AC_CHUNK) {
     const int c1 = min(c0 + AC_CHUNK, n_seen);
     float cmax = -INFINITY;
-    for (int e = c0 + warp; e < c1; e += AC_WARPS) {
+    for (int t = c0 + warp; t < c1; t += AC_WARPS) {
+      const int e = t < n_head ? t : t + shift;
       const TC* kr = kc + (((size_t)kt[e / page] * n_kv_heads + g) * page + (e % page)) * d;
       float dot = 0.0f;
       for (int i = lane; i < d; i += 32) dot = fmaf(q_s[i], nb_to_f32(kr[i]), dot);
       dot = nb_warp_sum(dot) * scale;
       if (softcap > 0.0f) dot = softcap * tanhf(dot * inv_cap);
-      if (lane == 0) scores[e - c0] = dot;
+      if (lane == 0) scores[t - c0] = dot;
       cmax = fmaxf(cmax, dot);
     }
     cmax = nb_block_max(cmax, red);
@@ -78,9 +95,10 @@ attention_capped_kernel(const TQ* q, const int* row_slot, const int* row_pos, co
     l_run = l_run * rescale + csum;
 #pragma unroll
     for (int a = 0; a < AC_DPL; ++a) acc[a] *= rescale;
-    for (int e = c0 + warp; e < c1; e += AC_WARPS) {
+    for (int t = c0 + warp; t < c1; t += AC_WARPS) {
+      const int e = t < n_head ? t : t + shift;
       const TC* vr = vc + (((size_t)vt[e / page] * n_kv_heads + g) * page + (e % page)) * dv;
-      const float p = scores[e - c0];
+      const float p = scores[t - c0];
 #pragma unroll
       for (int a = 0; a < AC_DPL; ++a) {
         const int i = lane + 32 * a;
@@ -104,7 +122,8 @@ attention_capped_kernel(const TQ* q, const int* row_slot, const int* row_pos, co
     fix = expf(m_run - m_f);
     denom = l_run * fix + expf(s - m_f);
   }
-  const float inv = denom > 0.0f ? fix / denom : 0.0f;
+  float inv = denom > 0.0f ? fix / denom : 0.0f;
+  if (gate != nullptr) inv *= nb_sigmoid(gate[(size_t)r * gate_stride + gate_col + h]);
   for (int i = lane; i < dv; i += 32) {
     float v = 0.0f;
 #pragma unroll
@@ -118,35 +137,51 @@ attention_capped_kernel(const TQ* q, const int* row_slot, const int* row_pos, co
 typedef __nv_bfloat16 bf16;
 
 // q: [n_rows][n_heads*d]; kc: [n_pages][n_kv_heads][page][d]; vc: [n_pages][n_kv_heads][page][dv];
-// sink: fp32 [n_heads] or null; softcap: 0 for none; out: [n_rows][n_heads*dv].
+// sink: fp32 [n_heads] or null; softcap: 0 for none; window / keep_first / chunk: 0 for none;
+// gate: fp32 [n_rows][gate_stride] or null; out: [n_rows][n_heads*dv].
+NB_EXPORT int nb_attention_masked(const void* q, int q_dtype, const int* row_slot, const int* row_pos,
+                                  const void* kc, const int* k_table, int k_max_pages,
+                                  const void* vc, const int* v_table, int v_max_pages,
+                                  int cache_dtype, int page, int n_heads, int n_kv_heads, int d,
+                                  int dv, const float* sink, void* out, int out_dtype, float scale,
+                                  float softcap, int window, int keep_first, int chunk,
+                                  const float* gate, int gate_stride, int gate_col, int n_rows,
+                                  cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(d >= 1 && d <= AC_MAXD && dv >= 1 && dv <= AC_MAXD, NB_ERR_UNSUPPORTED,
+             "attention_masked: heads of %d / %d are outside 1..%d", d, dv, AC_MAXD);
+  NB_REQUIRE(n_heads >= 1 && n_heads <= 65535 && n_kv_heads >= 1 && n_heads % n_kv_heads == 0 &&
+                 page > 0 && softcap >= 0.0f && window >= 0 && keep_first >= 0 && chunk >= 0 &&
+                 (gate == nullptr || gate_stride >= gate_col + n_heads),
+             NB_ERR_BAD_ARG, "attention_masked: bad sizes heads=%d/%d page=%d mask=%d/%d/%d",
+             n_heads, n_kv_heads, page, window, keep_first, chunk);
+  const dim3 grid(n_rows, n_heads);
+#define NB_AC(TQ, TC, TO)                                                                        \
+  NB_CUDA(nb_launch(attention_capped_kernel<TQ, TC, TO>, grid, dim3(AC_THREADS), 0, stream,      \
+                    (const TQ*)q, row_slot, row_pos, (const TC*)kc, k_table, k_max_pages,        \
+                    (const TC*)vc, v_table, v_max_pages, page, n_heads, n_kv_heads, d, dv, sink, \
+                    (TO*)out, scale, softcap, window, keep_first, chunk, gate, gate_stride,      \
+                    gate_col))
+  switch (q_dtype * 4 + cache_dtype * 2 + out_dtype) {
+    case 0: NB_AC(float, float, float); break;
+    case 7: NB_AC(bf16, bf16, bf16); break;
+    case 6: NB_AC(bf16, bf16, float); break;
+    default:
+      NB_REQUIRE(false, NB_ERR_UNSUPPORTED, "attention_masked: dtypes %d/%d/%d are not built",
+                 q_dtype, cache_dtype, out_dtype);
+  }
+#undef NB_AC
+  NB_CHECK_LAUNCH("attention_masked");
+  return 0;
+}
+
 NB_EXPORT int nb_attention_capped(const void* q, int q_dtype, const int* row_slot, const int* row_pos,
                                   const void* kc, const int* k_table, int k_max_pages,
                                   const void* vc, const int* v_table, int v_max_pages,
                                   int cache_dtype, int page, int n_heads, int n_kv_heads, int d,
                                   int dv, const float* sink, void* out, int out_dtype, float scale,
                                   float softcap, int n_rows, cudaStream_t stream) {
-  if (n_rows == 0) return 0;
-  NB_REQUIRE(d >= 1 && d <= AC_MAXD && dv >= 1 && dv <= AC_MAXD, NB_ERR_UNSUPPORTED,
-             "attention_capped: heads of %d / %d are outside 1..%d", d, dv, AC_MAXD);
-  NB_REQUIRE(n_heads >= 1 && n_heads <= 65535 && n_kv_heads >= 1 && n_heads % n_kv_heads == 0 &&
-                 page > 0 && softcap >= 0.0f,
-             NB_ERR_BAD_ARG, "attention_capped: bad sizes heads=%d/%d page=%d", n_heads,
-             n_kv_heads, page);
-  const dim3 grid(n_rows, n_heads);
-#define NB_AC(TQ, TC, TO)                                                                        \
-  NB_CUDA(nb_launch(attention_capped_kernel<TQ, TC, TO>, grid, dim3(AC_THREADS), 0, stream,      \
-                    (const TQ*)q, row_slot, row_pos, (const TC*)kc, k_table, k_max_pages,        \
-                    (const TC*)vc, v_table, v_max_pages, page, n_heads, n_kv_heads, d, dv, sink, \
-                    (TO*)out, scale, softcap))
-  switch (q_dtype * 4 + cache_dtype * 2 + out_dtype) {
-    case 0: NB_AC(float, float, float); break;
-    case 7: NB_AC(bf16, bf16, bf16); break;
-    case 6: NB_AC(bf16, bf16, float); break;
-    default:
-      NB_REQUIRE(false, NB_ERR_UNSUPPORTED, "attention_capped: dtypes %d/%d/%d are not built",
-                 q_dtype, cache_dtype, out_dtype);
-  }
-#undef NB_AC
-  NB_CHECK_LAUNCH("attention_capped");
-  return 0;
+  return nb_attention_masked(q, q_dtype, row_slot, row_pos, kc, k_table, k_max_pages, vc, v_table,
+                             v_max_pages, cache_dtype, page, n_heads, n_kv_heads, d, dv, sink, out,
+                             out_dtype, scale, softcap, 0, 0, 0, nullptr, 0, 0, n_rows, stream);
 }

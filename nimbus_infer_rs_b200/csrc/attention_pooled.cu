@@ -10,6 +10,9 @@
 //                           amplitude); queries go to a buffer of their own, keys into the K
 //                           plane of the paged store, and the key AS PROJECTED (no norm, no
 //                           rotation) into the V plane: the values are the keys.
+//   nb_qkv_norm_rope_append the same with values from columns of their own (any head size, a
+//                           plane and block table of their own) and the norm optional: what any
+//                           attention with rotated, optionally normed queries and keys needs.
 //   nb_pool_blocks          for every row that completes a block of `pool` tokens: the mean of
 //                           the block's keys as the store holds them, and of its values, into
 //                           entry pos / pool of a second paged store.
@@ -24,12 +27,13 @@ constexpr int QK_THREADS = 128;
 
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(QK_THREADS)
-qk_norm_rope_append_kernel(const float* src, int stride, int q_col, int k_col,
+qk_norm_rope_append_kernel(const float* src, int stride, int q_col, int k_col, int v_col,
                            const float* __restrict__ q_gamma, const float* __restrict__ k_gamma,
                            float eps, const float* __restrict__ freq, int rot_dims, float amplitude,
                            const int* row_slot, const int* row_pos, TQ* q_out, TC* kc, TC* vc,
-                           const int* block_table, int max_pages, int page, int n_heads,
-                           int n_kv_heads, int d, int write) {
+                           const int* block_table, int max_pages, const int* v_table,
+                           int v_max_pages, int page, int n_heads, int n_kv_heads, int d, int dv,
+                           int write) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
   const int r = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -42,25 +46,33 @@ qk_norm_rope_append_kernel(const float* src, int stride, int q_col, int k_col,
   const int pos = row_pos[r];
   const int half = rot_dims / 2;
   const float* row = src + (size_t)r * stride;
-  size_t cache_row = 0;
+  size_t cache_row = 0, v_row = 0;
   if (write) {
     const int page_id = block_table[(size_t)slot * max_pages + pos / page];
     cache_row = (size_t)page_id * n_kv_heads * page + (pos % page);   // + g * page, then * d
+    const int v_page = v_table[(size_t)slot * v_max_pages + pos / page];
+    v_row = (size_t)v_page * n_kv_heads * page + (pos % page);
   }
   for (int hh = warp; hh < n_heads + (write ? n_kv_heads : 0); hh += QK_THREADS / 32) {
     const bool is_q = hh < n_heads;
     const int g = hh - n_heads;
     const float* x = row + (is_q ? q_col + hh * d : k_col + g * d);
     const float* gamma = is_q ? q_gamma : k_gamma;
-    float ss = 0.0f;
-    for (int i = lane; i < d; i += 32) ss = fmaf(x[i], x[i], ss);
-    ss = nb_warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    float inv = 1.0f;
+    if (gamma != nullptr) {
+      float ss = 0.0f;
+      for (int i = lane; i < d; i += 32) ss = fmaf(x[i], x[i], ss);
+      ss = nb_warp_sum(ss);
+      inv = 1.0f / sqrtf(ss / (float)d + eps);
+    }
     TC* kd = is_q ? nullptr : kc + (cache_row + (size_t)g * page) * d;
-    TC* vd = is_q ? nullptr : vc + (cache_row + (size_t)g * page) * d;
     TQ* qd = qo + (size_t)hh * d;
     for (int i = lane; i < half; i += 32) {
-      const float a = x[i] * inv * gamma[i], b = x[i + half] * inv * gamma[i + half];
+      float a = x[i], b = x[i + half];
+      if (gamma != nullptr) {
+        a = a * inv * gamma[i];
+        b = b * inv * gamma[i + half];
+      }
       float s, c;
       sincosf((float)pos * freq[i], &s, &c);
       s *= amplitude;
@@ -75,12 +87,16 @@ qk_norm_rope_append_kernel(const float* src, int stride, int q_col, int k_col,
       }
     }
     for (int i = rot_dims + lane; i < d; i += 32) {
-      const float a = x[i] * inv * gamma[i];
+      const float a = gamma != nullptr ? x[i] * inv * gamma[i] : x[i];
       if (is_q) qd[i] = nb_from_f32<TQ>(a);
       else kd[i] = nb_from_f32<TC>(a);
     }
-    if (!is_q)
-      for (int i = lane; i < d; i += 32) vd[i] = nb_from_f32<TC>(x[i]);
+    if (!is_q) {
+      // the value: the key as projected, or columns of its own
+      const float* xv = v_col < 0 ? x : row + v_col + g * dv;
+      TC* vd = vc + (v_row + (size_t)g * page) * dv;
+      for (int i = lane; i < dv; i += 32) vd[i] = nb_from_f32<TC>(xv[i]);
+    }
   }
 }
 
@@ -254,6 +270,42 @@ typedef __nv_bfloat16 bf16;
 // q_out: [n_rows][n_heads*d]; kc, vc: planes [n_pages][n_kv_heads][page][d]; freq: fp32
 // [rot_dims/2] (null when rot_dims is 0).  write == 0: queries only (a reader of another
 // layer's store).
+// The general form.  q_gamma / k_gamma: null for no norm.  v_col < 0: the values are the keys as
+// projected (dv = d, into `vc` by the keys' block table); else the values are columns v_col ..
+// of `src` (n_kv_heads heads of dv), written to the plane `vc`, whose pages `v_table` lists (the
+// keys' table again when keys and values share a store of two planes).
+NB_EXPORT int nb_qkv_norm_rope_append(const float* src, int stride, int q_col, int k_col, int v_col,
+                                      const float* q_gamma, const float* k_gamma, float eps,
+                                      const float* freq, int rot_dims, float amplitude,
+                                      const int* row_slot, const int* row_pos, void* q_out,
+                                      int q_dtype, void* kc, void* vc, int cache_dtype,
+                                      const int* block_table, int max_pages, const int* v_table,
+                                      int v_max_pages, int page, int n_heads, int n_kv_heads, int d,
+                                      int dv, int write, int n_rows, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(n_heads > 0 && n_kv_heads > 0 && d > 0 && dv > 0 && page > 0 && rot_dims >= 0 &&
+                 rot_dims % 2 == 0 && rot_dims <= d && (rot_dims == 0 || freq != nullptr) &&
+                 (v_col >= 0 || dv == d) && (q_gamma == nullptr) == (k_gamma == nullptr),
+             NB_ERR_BAD_ARG, "qkv_norm_rope_append: bad sizes heads=%d/%d d=%d/%d rot=%d", n_heads,
+             n_kv_heads, d, dv, rot_dims);
+  if (v_table == nullptr) { v_table = block_table; v_max_pages = max_pages; }
+#define NB_QK(TQ, TC)                                                                             \
+  NB_CUDA(nb_launch(qk_norm_rope_append_kernel<TQ, TC>, dim3(n_rows), dim3(QK_THREADS), 0, stream, \
+                    src, stride, q_col, k_col, v_col, q_gamma, k_gamma, eps, freq, rot_dims,      \
+                    amplitude, row_slot, row_pos, (TQ*)q_out, (TC*)kc, (TC*)vc, block_table,      \
+                    max_pages, v_table, v_max_pages, page, n_heads, n_kv_heads, d, dv, write))
+  switch (q_dtype * 2 + cache_dtype) {
+    case 0: NB_QK(float, float); break;
+    case 1: NB_QK(float, bf16); break;
+    case 2: NB_QK(bf16, float); break;
+    case 3: NB_QK(bf16, bf16); break;
+    default: NB_REQUIRE(false, NB_ERR_BAD_ARG, "qkv_norm_rope_append: unknown dtypes %d/%d", q_dtype, cache_dtype);
+  }
+#undef NB_QK
+  NB_CHECK_LAUNCH("qkv_norm_rope_append");
+  return 0;
+}
+
 NB_EXPORT int nb_qk_norm_rope_append(const float* src, int stride, int q_col, int k_col,
                                      const float* q_gamma, const float* k_gamma, float eps,
                                      const float* freq, int rot_dims, float amplitude,
@@ -262,26 +314,12 @@ NB_EXPORT int nb_qk_norm_rope_append(const float* src, int stride, int q_col, in
                                      const int* block_table, int max_pages, int page, int n_heads,
                                      int n_kv_heads, int d, int write, int n_rows,
                                      cudaStream_t stream) {
-  if (n_rows == 0) return 0;
-  NB_REQUIRE(n_heads > 0 && n_kv_heads > 0 && d > 0 && page > 0 && rot_dims >= 0 &&
-                 rot_dims % 2 == 0 && rot_dims <= d && (rot_dims == 0 || freq != nullptr),
-             NB_ERR_BAD_ARG, "qk_norm_rope_append: bad sizes heads=%d/%d d=%d rot=%d", n_heads,
-             n_kv_heads, d, rot_dims);
-#define NB_QK(TQ, TC)                                                                             \
-  NB_CUDA(nb_launch(qk_norm_rope_append_kernel<TQ, TC>, dim3(n_rows), dim3(QK_THREADS), 0, stream, \
-                    src, stride, q_col, k_col, q_gamma, k_gamma, eps, freq, rot_dims, amplitude,  \
-                    row_slot, row_pos, (TQ*)q_out, (TC*)kc, (TC*)vc, block_table, max_pages,      \
-                    page, n_heads, n_kv_heads, d, write))
-  switch (q_dtype * 2 + cache_dtype) {
-    case 0: NB_QK(float, float); break;
-    case 1: NB_QK(float, bf16); break;
-    case 2: NB_QK(bf16, float); break;
-    case 3: NB_QK(bf16, bf16); break;
-    default: NB_REQUIRE(false, NB_ERR_BAD_ARG, "qk_norm_rope_append: unknown dtypes %d/%d", q_dtype, cache_dtype);
-  }
-#undef NB_QK
-  NB_CHECK_LAUNCH("qk_norm_rope_append");
-  return 0;
+  NB_REQUIRE(q_gamma != nullptr && k_gamma != nullptr, NB_ERR_BAD_ARG,
+             "qk_norm_rope_append: a norm without its weight");
+  return nb_qkv_norm_rope_append(src, stride, q_col, k_col, -1, q_gamma, k_gamma, eps, freq, rot_dims,
+                                 amplitude, row_slot, row_pos, q_out, q_dtype, kc, vc, cache_dtype,
+                                 block_table, max_pages, block_table, max_pages, page, n_heads,
+                                 n_kv_heads, d, d, write, n_rows, stream);
 }
 
 NB_EXPORT int nb_pool_blocks(const int* row_slot, const int* row_pos, const void* kc, const void* vc,

@@ -19,7 +19,8 @@ enum NbDType : int { NB_F32 = 0, NB_BF16 = 1 };
 enum NbAct : int { NB_ACT_NONE = 0, NB_ACT_GELU_TANH = 1, NB_ACT_GELU_ERF = 2, NB_ACT_SILU = 3,
                    NB_ACT_RELU2 = 4,   // the square of relu
                    NB_ACT_TANH = 5, NB_ACT_XIELU = 6,     // row passes only (nb_act_rows)
-                   NB_ACT_RELU = 7 };                     // row passes and gates (nb_glu_rows)
+                   NB_ACT_RELU = 7,                       // row passes and gates (nb_glu_rows)
+                   NB_ACT_SWISH_CLAMP = 8 };              // gated halves only (nb_gate_up)
 
 // Error codes above the range of cudaError_t.
 #define NB_ERR_BAD_ARG 10001
@@ -213,6 +214,22 @@ __device__ __forceinline__ float nb_apply_act(float x, int act) {
   if (act == NB_ACT_RELU2) return x > 0.0f ? x * x : 0.0f;
   if (act == NB_ACT_RELU) return fmaxf(x, 0.0f);
   return x;
+}
+
+// The two halves of a gated feed-forward, combined: act(gate) * up, or with NB_ACT_SWISH_CLAMP
+// and its bound L = `param`:  g = min(gate, L), u = clamp(up, -L, L),  g * sigmoid(alpha g) * (u + 1)
+// with alpha = NB_SWISH_ALPHA.  FAST: the hardware exponential and reciprocal (bf16 epilogues).
+#define NB_SWISH_ALPHA 1.702f
+template <bool FAST>
+__device__ __forceinline__ float nb_gate_up(float gate, float up, int act, float param) {
+  if (act == NB_ACT_SWISH_CLAMP) {
+    const float g = fminf(gate, param);
+    const float u = fminf(fmaxf(up, -param), param);
+    const float s = FAST ? __fdividef(g, 1.0f + __expf(-NB_SWISH_ALPHA * g))
+                         : g / (1.0f + expf(-NB_SWISH_ALPHA * g));
+    return s * (u + 1.0f);
+  }
+  return (FAST ? nb_apply_act_fast(gate, act) : nb_apply_act(gate, act)) * up;
 }
 
 __device__ __forceinline__ float nb_warp_sum(float v) {

@@ -4,6 +4,8 @@
 //   nb_moe_route    scores = softmax(router logits) over all experts (fp32); the `top`
 //                   largest per row (of equal scores the lower index), with their scores as
 //                   weights (optionally renormalised to sum 1)
+//   nb_moe_route_sigmoid  scores = sigmoid(logits); chosen by score + bias among the experts of
+//                   the best groups; weights are the scores, renormalised and scaled
 //   nb_moe_group    the (row, choice) pairs grouped by expert: offsets[e] .. offsets[e+1] are
 //                   the places of expert e's pairs, order[place] = pair, place[pair] = place
 //   nb_moe_gemm     a product per expert over its group of rows, tiled; with two weight
@@ -21,6 +23,29 @@
 namespace {
 
 constexpr int ROUTE_MAX_PER_LANE = 32;   // n_experts <= 32 * this
+
+// The `top` largest of the lane-distributed values v (entry i of a lane is expert lane + 32 i;
+// NEG marks "none" or "taken"), of equal values the lower index: the k-th winner's index goes to
+// out_e[k] of every lane and its entry is marked taken.
+__device__ __forceinline__ void route_take_best(float (&v)[ROUTE_MAX_PER_LANE], int lane, float neg,
+                                                float& best, int& best_e) {
+  best = neg;
+  best_e = 0x7fffffff;
+#pragma unroll
+  for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    if (v[i] > best) { best = v[i]; best_e = e; }     // ascending e within a lane: first wins
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+    if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+  }
+#pragma unroll
+  for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
+    if (lane + 32 * i == best_e) v[i] = neg;
+}
 
 __global__ void moe_route_kernel(const float* logits, int stride, int col, const int* row_slot,
                                  int n_rows, int n_experts, int top, int renormalize, int* idx,
@@ -58,22 +83,9 @@ __global__ void moe_route_kernel(const float* logits, int stride, int col, const
   const float inv = 1.0f / sum;
   float chosen_sum = 0.0f;
   for (int k = 0; k < top; ++k) {
-    float best = -1.0f;
-    int best_e = 0x7fffffff;
-#pragma unroll
-    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
-      const int e = lane + 32 * i;
-      if (v[i] > best) { best = v[i]; best_e = e; }     // ascending e within a lane: first wins
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-    }
-#pragma unroll
-    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
-      if (lane + 32 * i == best_e) v[i] = -1.0f;
+    float best;
+    int best_e;
+    route_take_best(v, lane, -1.0f, best, best_e);
     const float s = best * inv;
     chosen_sum += s;
     if (lane == 0) {
@@ -85,6 +97,100 @@ __global__ void moe_route_kernel(const float* logits, int stride, int col, const
     __syncwarp();
     for (int k = lane; k < top; k += 32) weight[(size_t)r * top + k] /= chosen_sum;
   }
+}
+
+// Routing by sigmoid scores with a choice bias and groups of experts.  s = sigmoid(z); the choice
+// score of expert e is c_e = s_e + bias_e (bias may be null).  With n_groups > 1 the experts form
+// n_groups equal groups of neighbours; a group's score is the sum of its `group_top` largest
+// choice scores; only the experts of the `keep_groups` groups with the largest scores (of equal
+// scores the lower group) can be chosen.  The `top` allowed experts with the largest choice
+// scores are chosen (of equal scores the lower index); their weights are their s (without the
+// bias), divided by (their sum + norm_eps) when `renormalize`, times `out_scale`.
+__global__ void moe_route_sigmoid_kernel(const float* logits, int stride, int col,
+                                         const float* __restrict__ bias, const int* row_slot,
+                                         int n_rows, int n_experts, int top, int n_groups,
+                                         int keep_groups, int group_top, int renormalize,
+                                         float norm_eps, float out_scale, int* idx, float* weight) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  if (row_slot[r] < 0) {
+    for (int k = lane; k < top; k += 32) {
+      idx[(size_t)r * top + k] = -1;
+      weight[(size_t)r * top + k] = 0.0f;
+    }
+    return;
+  }
+  const float* z = logits + (size_t)r * stride + col;
+  float s[ROUTE_MAX_PER_LANE], c[ROUTE_MAX_PER_LANE];
+#pragma unroll
+  for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    s[i] = e < n_experts ? 1.0f / (1.0f + expf(-z[e])) : 0.0f;
+    c[i] = e < n_experts ? s[i] + (bias != nullptr ? bias[e] : 0.0f) : -INFINITY;
+  }
+  if (n_groups > 1 && keep_groups < n_groups) {
+    // group scores: lane g (+ 32 j) owns group g; every group's `group_top` largest are taken
+    // from a copy of the choice scores, one group after the other
+    const int per = n_experts / n_groups;
+    float gs[ROUTE_MAX_PER_LANE];     // gs[j]: score of group lane + 32 j
+#pragma unroll
+    for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) gs[j] = -INFINITY;
+    for (int g = 0; g < n_groups; ++g) {
+      float t[ROUTE_MAX_PER_LANE];
+#pragma unroll
+      for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        t[i] = (e >= g * per && e < (g + 1) * per) ? c[i] : -INFINITY;
+      }
+      float total = 0.0f;
+      for (int k = 0; k < group_top && k < per; ++k) {
+        float best;
+        int best_e;
+        route_take_best(t, lane, -INFINITY, best, best_e);
+        total += best;
+      }
+#pragma unroll
+      for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j)
+        if (lane + 32 * j == g) gs[j] = total;
+    }
+    // the kept groups, as a bit per group held by the lane that owns it
+    unsigned kept_bits = 0u;          // bit j: group lane + 32 j is kept
+    for (int k = 0; k < keep_groups; ++k) {
+      float best;
+      int best_g;
+      route_take_best(gs, lane, -INFINITY, best, best_g);
+      if (best_g != 0x7fffffff && (best_g & 31) == lane) kept_bits |= 1u << (best_g >> 5);
+    }
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      const int g = min(e, n_experts - 1) / per;        // every lane takes part in the shuffle
+      const unsigned bits = __shfl_sync(0xffffffffu, kept_bits, g & 31);
+      if (e < n_experts && !((bits >> (g >> 5)) & 1u)) c[i] = -INFINITY;
+    }
+  }
+  float chosen_sum = 0.0f;
+  for (int k = 0; k < top; ++k) {
+    float best;
+    int best_e;
+    route_take_best(c, lane, -INFINITY, best, best_e);
+    float sv = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
+      if (lane + 32 * i == best_e) sv = s[i];
+    sv = nb_warp_sum(sv);             // one lane holds it, the others zero
+    chosen_sum += sv;
+    if (lane == 0) {
+      idx[(size_t)r * top + k] = best_e == 0x7fffffff ? -1 : best_e;
+      weight[(size_t)r * top + k] = sv;
+    }
+  }
+  __syncwarp();
+  const float f = (renormalize ? 1.0f / (chosen_sum + norm_eps) : 1.0f) * out_scale;
+  for (int k = lane; k < top; k += 32) weight[(size_t)r * top + k] *= f;
 }
 
 // One CTA.  counts and cursors live in shared memory ([n_experts] ints each).
@@ -131,7 +237,7 @@ template <typename TX, typename TW, typename TY, bool DUAL>
 __global__ void __launch_bounds__(GEMM_THREADS)
 moe_gemm_kernel(const TX* x, int x_stride, const int* order, int row_div, const int* offsets,
                 int n_experts, const TW* __restrict__ W, const TW* __restrict__ W2, TY* y,
-                int y_stride, int N, int K, int act) {
+                int y_stride, int N, int K, int act, float act_param) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
   __shared__ float As[TM][TK + 1];
@@ -206,7 +312,7 @@ moe_gemm_kernel(const TX* x, int x_stride, const int* order, int row_div, const 
       const int n = n0 + tx + 16 * c;
       if (n >= N) continue;
       float v = acc[i][c];
-      if (DUAL) v = nb_apply_act(v, act) * acc2[i][c];
+      if (DUAL) v = nb_gate_up<false>(v, acc2[i][c], act, act_param);
       else v = nb_apply_act(v, act);
       y[(size_t)p * y_stride + n] = nb_from_f32<TY>(v);
     }
@@ -247,6 +353,30 @@ NB_EXPORT int nb_moe_route(const float* logits, int stride, int col, const int* 
   return 0;
 }
 
+// bias: fp32 [n_experts] or null; n_groups <= 1: no groups.
+NB_EXPORT int nb_moe_route_sigmoid(const float* logits, int stride, int col, const float* bias,
+                                   const int* row_slot, int n_rows, int n_experts, int top,
+                                   int n_groups, int keep_groups, int group_top, int renormalize,
+                                   float norm_eps, float out_scale, int* idx, float* weight,
+                                   cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(n_experts >= 1 && n_experts <= 32 * ROUTE_MAX_PER_LANE, NB_ERR_UNSUPPORTED,
+             "moe_route_sigmoid: %d experts are outside 1..%d", n_experts, 32 * ROUTE_MAX_PER_LANE);
+  NB_REQUIRE(top >= 1 && top <= n_experts, NB_ERR_BAD_ARG, "moe_route_sigmoid: top=%d of %d experts",
+             top, n_experts);
+  NB_REQUIRE(col >= 0 && stride >= col + n_experts, NB_ERR_BAD_ARG, "moe_route_sigmoid: bad columns");
+  if (n_groups > 1)
+    NB_REQUIRE(n_experts % n_groups == 0 && keep_groups >= 1 && keep_groups <= n_groups &&
+                   group_top >= 1 && keep_groups * (n_experts / n_groups) >= top,
+               NB_ERR_BAD_ARG, "moe_route_sigmoid: %d groups (keep %d, top %d of each) of %d experts, top=%d",
+               n_groups, keep_groups, group_top, n_experts, top);
+  NB_CUDA(nb_launch(moe_route_sigmoid_kernel, dim3((n_rows + 3) / 4), dim3(128), 0, stream, logits,
+                    stride, col, bias, row_slot, n_rows, n_experts, top, n_groups, keep_groups,
+                    group_top, renormalize, norm_eps, out_scale, idx, weight));
+  NB_CHECK_LAUNCH("moe_route_sigmoid");
+  return 0;
+}
+
 NB_EXPORT int nb_moe_group(const int* idx, int n_pairs, int n_experts, int* offsets, int* order,
                            int* place, cudaStream_t stream) {
   NB_REQUIRE(n_pairs >= 0 && n_experts >= 1 && n_experts <= 4096, NB_ERR_BAD_ARG,
@@ -268,7 +398,7 @@ NB_EXPORT int nb_moe_gemm_tiles(int n_pairs, int n_experts) {
 NB_EXPORT int nb_moe_gemm(const void* x, int x_dtype, int x_stride, const int* order, int row_div,
                           const int* offsets, int n_experts, int n_pairs, const void* W,
                           const void* W2, int w_dtype, void* y, int y_dtype, int y_stride, int N,
-                          int K, int act, cudaStream_t stream) {
+                          int K, int act, float act_param, cudaStream_t stream) {
   if (n_pairs == 0) return 0;
   NB_REQUIRE(N > 0 && K > 0 && n_experts >= 1 && row_div >= 1, NB_ERR_BAD_ARG,
              "moe_gemm: bad sizes N=%d K=%d experts=%d", N, K, n_experts);
@@ -279,11 +409,11 @@ NB_EXPORT int nb_moe_gemm(const void* x, int x_dtype, int x_stride, const int* o
     if (W2 != nullptr)                                                                             \
       NB_CUDA(nb_launch(moe_gemm_kernel<TX, TW, TY, true>, grid, dim3(GEMM_THREADS), 0, stream,    \
                         (const TX*)x, x_stride, order, row_div, offsets, n_experts, (const TW*)W,  \
-                        (const TW*)W2, (TY*)y, y_stride, N, K, act));                              \
+                        (const TW*)W2, (TY*)y, y_stride, N, K, act, act_param));                              \
     else                                                                                           \
       NB_CUDA(nb_launch(moe_gemm_kernel<TX, TW, TY, false>, grid, dim3(GEMM_THREADS), 0, stream,   \
                         (const TX*)x, x_stride, order, row_div, offsets, n_experts, (const TW*)W,  \
-                        (const TW*)W2, (TY*)y, y_stride, N, K, act));                              \
+                        (const TW*)W2, (TY*)y, y_stride, N, K, act, act_param));                              \
   } while (0)
   const int key = x_dtype * 4 + w_dtype * 2 + y_dtype;
   switch (key) {

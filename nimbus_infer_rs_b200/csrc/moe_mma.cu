@@ -43,7 +43,7 @@ template <typename S, bool DUAL, typename TX, typename TY>
 __global__ void __launch_bounds__(S::THREADS)
 moe_mma_kernel(const TX* x, int x_stride, const int* order, int row_div, const int* offsets,
                int n_experts, const bf16* __restrict__ W, const bf16* __restrict__ W2, TY* y,
-               int y_stride, int N, int K, int act, int uniform_rows, int x_gcol, int y_gcol,
+               int y_stride, int N, int K, int act, float act_param, int uniform_rows, int x_gcol, int y_gcol,
                const int* row_slot, const float* gate, int gate_stride, int gate_col) {
   constexpr int BM = S::BM, THREADS = S::THREADS, STAGES = S::STAGES, MI = S::MI, NJ = S::NJ;
   nb_grid_dependency_wait();
@@ -214,7 +214,7 @@ moe_mma_kernel(const TX* x, int x_stride, const int* order, int row_div, const i
           const int n = n0 + col_w + nt * 8 + 2 * t4 + c;
           if (n >= N) continue;
           float v = acc[mi][nt][2 * half + c];
-          if (DUAL) v = nb_apply_act_fast(v, act) * acc2[mi][nt][2 * half + c];
+          if (DUAL) v = nb_gate_up<true>(v, acc2[mi][nt][2 * half + c], act, act_param);
           else v = nb_apply_act_fast(v, act);
           y[(size_t)p * y_stride + n] = nb_from_f32<TY>(scale == 0.0f ? 0.0f : v * scale);
         }
@@ -239,7 +239,7 @@ int tiles_of(int places, int groups) {
 template <typename S, bool DUAL, typename TX, typename TY>
 int launch(int tiles, cudaStream_t stream, const TX* x, int x_stride, const int* order, int row_div,
            const int* offsets, int n_experts, const bf16* W, const bf16* W2, TY* y, int y_stride,
-           int N, int K, int act, Uniform u = Uniform()) {
+           int N, int K, int act, float act_param, Uniform u = Uniform()) {
   const size_t smem = (size_t)S::STAGES * (S::BM + BN * (DUAL ? 2 : 1)) * LD * sizeof(bf16);
   static bool set = false;
   if (!set) {
@@ -250,7 +250,7 @@ int launch(int tiles, cudaStream_t stream, const TX* x, int x_stride, const int*
   const dim3 grid(tiles, (N + BN - 1) / BN);
   NB_REQUIRE(grid.y <= 65535, NB_ERR_UNSUPPORTED, "grouped product: %d outputs are too many", N);
   NB_CUDA(nb_launch(moe_mma_kernel<S, DUAL, TX, TY>, grid, dim3(S::THREADS), smem, stream, x, x_stride,
-                    order, row_div, offsets, n_experts, W, W2, y, y_stride, N, K, act, u.rows, u.x_gcol,
+                    order, row_div, offsets, n_experts, W, W2, y, y_stride, N, K, act, act_param, u.rows, u.x_gcol,
                     u.y_gcol, u.row_slot, u.gate, u.gate_stride, u.gate_col));
   return 0;
 }
@@ -266,7 +266,7 @@ NB_EXPORT int nb_moe_gemm_mma_supported(int x_dtype, int w_dtype, int x_stride, 
 
 NB_EXPORT int nb_moe_gemm_mma(const void* x, int x_stride, const int* order, int row_div,
                               const int* offsets, int n_experts, int n_pairs, const void* W,
-                              const void* W2, void* y, int y_dtype, int y_stride, int N, int K, int act,
+                              const void* W2, void* y, int y_dtype, int y_stride, int N, int K, int act, float act_param,
                               cudaStream_t stream) {
   if (n_pairs == 0) return 0;
   NB_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && x_stride % 8 == 0 && n_experts >= 1 && row_div >= 1,
@@ -281,7 +281,7 @@ NB_EXPORT int nb_moe_gemm_mma(const void* x, int x_stride, const int* order, int
   const bf16* w2 = (const bf16*)W2;
 #define NB_GO(S_, DUAL_, TY_)                                                                       \
   rc = launch<S_, DUAL_, bf16, TY_>(tiles_of<S_>(n_pairs, n_experts), stream, xb, x_stride, order,   \
-                                    row_div, offsets, n_experts, w, w2, (TY_*)y, y_stride, N, K, act)
+                                    row_div, offsets, n_experts, w, w2, (TY_*)y, y_stride, N, K, act, act_param)
   if (n_pairs <= SMALL_MAX_PLACES) {
     if (y_dtype == NB_BF16) { if (W2) NB_GO(Small, true, bf16); else NB_GO(Small, false, bf16); }
     else { if (W2) NB_GO(Small, true, float); else NB_GO(Small, false, float); }
@@ -320,7 +320,7 @@ NB_EXPORT int nb_head_linear_mma(const void* x, int x_dtype, int x_stride, int x
 #define NB_GO(S_, TX_)                                                                               \
   rc = launch<S_, false, TX_, bf16>(((n_rows + S_::BM - 1) / S_::BM) * n_heads, stream,               \
                                     (const TX_*)x + x_col, x_stride, nullptr, 1, nullptr, n_heads,    \
-                                    (const bf16*)W, nullptr, (bf16*)y, y_stride, n_out, n_in, 0, u)
+                                    (const bf16*)W, nullptr, (bf16*)y, y_stride, n_out, n_in, 0, 0.0f, u)
   if (n_rows <= 16) {
     if (x_dtype == NB_F32) NB_GO(Small, float); else NB_GO(Small, bf16);
   } else {

@@ -41,7 +41,7 @@ template <bool DUAL, typename TY>
 __global__ void __launch_bounds__(THREADS)
 moe_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
               const __grid_constant__ CUtensorMap map_w2, const int* offsets, int n_experts, TY* y,
-              int y_stride, int N, int K, int act, int* err_word) {
+              int y_stride, int N, int K, int act, float act_param, int* err_word) {
   using L = Layout<DUAL>;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
@@ -155,7 +155,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__
           tc05_wait_ld();
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            v[j] = __float_as_uint(nb_apply_act_fast(__uint_as_float(v[j]), act) * __uint_as_float(w[j]));
+            v[j] = __float_as_uint(nb_gate_up<true>(__uint_as_float(v[j]), __uint_as_float(w[j]), act, act_param));
         }
         tc05_wait_ld();
         if (!DUAL && act != NB_ACT_NONE) {
@@ -241,7 +241,7 @@ int* error_word() {
 
 template <bool DUAL, typename TY>
 int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2, dim3 grid,
-           const int* offsets, int n_experts, TY* y, int y_stride, int N, int K, int act,
+           const int* offsets, int n_experts, TY* y, int y_stride, int N, int K, int act, float act_param,
            cudaStream_t stream) {
   auto kern = moe_tc_kernel<DUAL, TY>;
   const int smem = Layout<DUAL>::TOTAL;
@@ -251,7 +251,7 @@ int launch(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mw2,
     configured = true;
   }
   NB_CUDA(nb_launch(kern, grid, dim3(THREADS), (size_t)smem, stream, mx, mw, mw2, offsets, n_experts, y,
-                    y_stride, N, K, act, error_word()));
+                    y_stride, N, K, act, act_param, error_word()));
   return 0;
 }
 
@@ -285,7 +285,7 @@ NB_EXPORT int nb_moe_gather(const void* x, int x_stride, const int* order, int r
 // null); y: [>= n_places][y_stride].
 NB_EXPORT int nb_moe_gemm_tc(const void* x, int x_rows, const int* offsets, int n_experts, int n_places,
                              const void* W, const void* W2, void* y, int y_dtype, int y_stride, int N,
-                             int K, int act, cudaStream_t stream) {
+                             int K, int act, float act_param, cudaStream_t stream) {
   if (n_places == 0) return 0;
   NB_REQUIRE(nb_moe_gemm_tc_supported(NB_BF16, NB_BF16, x_rows, n_experts, N, K), NB_ERR_UNSUPPORTED,
              "moe_gemm_tc: shape not supported (rows=%d experts=%d N=%d K=%d)", x_rows, n_experts, N, K);
@@ -306,11 +306,11 @@ NB_EXPORT int nb_moe_gemm_tc(const void* x, int x_rows, const int* offsets, int 
   const dim3 grid(tiles, (N + BN - 1) / BN);
   NB_REQUIRE(grid.y <= 65535, NB_ERR_UNSUPPORTED, "moe_gemm_tc: %d outputs are too many", N);
   if (y_dtype == NB_BF16)
-    rc = W2 ? launch<true, bf16>(mx, mw, mw2, grid, offsets, n_experts, (bf16*)y, y_stride, N, K, act, stream)
-            : launch<false, bf16>(mx, mw, mw2, grid, offsets, n_experts, (bf16*)y, y_stride, N, K, act, stream);
+    rc = W2 ? launch<true, bf16>(mx, mw, mw2, grid, offsets, n_experts, (bf16*)y, y_stride, N, K, act, act_param, stream)
+            : launch<false, bf16>(mx, mw, mw2, grid, offsets, n_experts, (bf16*)y, y_stride, N, K, act, act_param, stream);
   else if (y_dtype == NB_F32)
-    rc = W2 ? launch<true, float>(mx, mw, mw2, grid, offsets, n_experts, (float*)y, y_stride, N, K, act, stream)
-            : launch<false, float>(mx, mw, mw2, grid, offsets, n_experts, (float*)y, y_stride, N, K, act, stream);
+    rc = W2 ? launch<true, float>(mx, mw, mw2, grid, offsets, n_experts, (float*)y, y_stride, N, K, act, act_param, stream)
+            : launch<false, float>(mx, mw, mw2, grid, offsets, n_experts, (float*)y, y_stride, N, K, act, act_param, stream);
   else
     NB_REQUIRE(false, NB_ERR_BAD_ARG, "moe_gemm_tc: unknown output dtype %d", y_dtype);
   if (rc) return rc;

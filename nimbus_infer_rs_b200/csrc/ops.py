@@ -16,12 +16,15 @@ import torch
 
 ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_SILU, ACT_RELU2, ACT_TANH, ACT_XIELU = 0, 1, 2, 3, 4, 5, 6
 ACT_RELU = 7
+ACT_SWISH_CLAMP = 8    # g = min(gate, L), u = clamp(up, -L, L): g * sigmoid(1.702 g) * (u + 1); gated halves only
 # what a dense product's epilogue can apply
 ACTIVATIONS = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "gelu_erf": ACT_GELU_ERF}
 # what the experts' first product (routed experts) can apply
 GATE_ACTIVATIONS = {**ACTIVATIONS, "silu": ACT_SILU, "relu2": ACT_RELU2}
 # what the gate of a gated dense feed-forward can apply (`glu_rows`)
-GLU_ACTIVATIONS = {**GATE_ACTIVATIONS, "relu": ACT_RELU}
+GLU_ACTIVATIONS = {**GATE_ACTIVATIONS, "relu": ACT_RELU, "swish_clamp": ACT_SWISH_CLAMP}
+# combiners of a gated half that take a number (the bound of ``swish_clamp``)
+PARAM_ACTIVATIONS = {"swish_clamp"}
 # what a pass over fp32 rows can apply (`act_rows`): those, and activations with learned numbers
 ROW_ACTIVATIONS = {"tanh": ACT_TANH, "xielu": ACT_XIELU}
 
@@ -185,6 +188,29 @@ class CudaBackend:
         self._call("nb_embed_pos", _ptr(tokens), _ptr(pos), _ptr(wte), _ptr(wpe),
                    dtype_code(wte.dtype), _ptr(out), n, d, float(scale), self._stream())
 
+    def embed_hashed(self, tokens, pos, row_slot, wte, pair, last, out, scale, mul_prev, mul_cur,
+                     n_buckets):
+        """``out[r] = scale * wte[token] + pair[(prev * mul_prev + token * mul_cur) % n_buckets]``
+        (row ``n_buckets`` of ``pair`` for a sequence's first token); ``prev`` is the row before
+        in the step or, at the start of a continued sequence, ``last[slot, 0]`` (fp32 state)."""
+        _check(tokens, "tokens", torch.int32, 1)
+        _check(wte, "wte", None, 2)
+        _check(pair, "pair", wte.dtype, 2)
+        _check(last, "last", torch.float32, 2)
+        _check(out, "out", torch.float32, 2)
+        n, d = out.shape
+        if tokens.numel() < n or wte.shape[1] != d or pair.shape != (n_buckets + 1, d):
+            raise KernelError("embed_hashed: shapes do not agree")
+        self._call("nb_embed_hashed", _ptr(tokens), _ptr(pos), _ptr(row_slot), _ptr(wte), _ptr(pair),
+                   dtype_code(wte.dtype), _ptr(last), last.stride(0), _ptr(out), n, d, float(scale),
+                   int(mul_prev), int(mul_cur), int(n_buckets), self._stream())
+
+    def last_token(self, tokens, pos, row_slot, last, n_rows):
+        """``last[slot, 0]`` = the token of each sequence's last row in this step."""
+        _check(last, "last", torch.float32, 2)
+        self._call("nb_last_token", _ptr(tokens), _ptr(pos), _ptr(row_slot), _ptr(last),
+                   last.stride(0), int(n_rows), self._stream())
+
     def layernorm(self, x, gamma, beta, eps, out, rows=None):
         _check(x, "x", torch.float32, 2)
         _check(gamma, "gamma", torch.float32, 1)
@@ -215,10 +241,18 @@ class CudaBackend:
         self._call("nb_rmsnorm", _ptr(x), x.shape[1], x_col, _ptr(rows), _ptr(gamma), _ptr(out),
                    dtype_code(out.dtype), n, d, eps, self._stream())
 
+    def ln_add(self, y, gamma, eps, residual, next_gamma, next_eps, out_next, out_cast):
+        """:meth:`rms_add` with both norms centred: ``residual += (y - mean) / sqrt(var + eps) *
+        gamma`` (a layer norm with a weight and no shift), ``out_next`` likewise."""
+        self._norm_add("nb_ln_add", y, gamma, eps, residual, next_gamma, next_eps, out_next, out_cast)
+
     def rms_add(self, y, gamma, eps, residual, next_gamma, next_eps, out_next, out_cast):
         """``residual += y / sqrt(mean(y^2) + eps) * gamma`` per row (fp32), and in the same pass,
         where asked for, ``out_next = rms-norm(residual) * next_gamma`` and ``out_cast =
         residual`` in the activation type."""
+        self._norm_add("nb_rms_add", y, gamma, eps, residual, next_gamma, next_eps, out_next, out_cast)
+
+    def _norm_add(self, fn, y, gamma, eps, residual, next_gamma, next_eps, out_next, out_cast):
         _check(y, "y", torch.float32, 2)
         _check(residual, "residual", torch.float32, 2)
         _check(gamma, "gamma", torch.float32, 1)
@@ -236,7 +270,7 @@ class CudaBackend:
             raise KernelError("rms_add: the two outputs differ in type")
         if out_next is not None:
             _check(next_gamma, "next_gamma", torch.float32, 1)
-        self._call("nb_rms_add", _ptr(y), _ptr(gamma), float(eps), _ptr(residual),
+        self._call(fn, _ptr(y), _ptr(gamma), float(eps), _ptr(residual),
                    _ptr(next_gamma if out_next is not None else None), float(next_eps),
                    _ptr(out_next), _ptr(out_cast), code, n, d, self._stream())
 
@@ -678,6 +712,67 @@ class CudaBackend:
                    kv.block_table.shape[1], kv.page, n_heads, G, d, 1 if write else 0, n,
                    self._stream())
 
+    def qkv_norm_rope_append(self, src, q_col, k_col, v_col, q_gamma, k_gamma, eps, freq, rot_dims,
+                             amplitude, layout, k_store, v_store, n_heads, value_dim, q_out, write):
+        """Queries, keys and values of the fp32 rows ``src`` made ready: per head an optional RMS
+        norm (``q_gamma`` / ``k_gamma`` or ``None``) and the rotation of the first ``rot_dims``
+        numbers of queries and keys; queries to ``q_out``, keys to the K plane of ``k_store``,
+        values (columns ``v_col ..``, heads of ``value_dim``) to the V plane of ``k_store`` when
+        ``v_store`` is the same store, else to the one plane of ``v_store``."""
+        _check(src, "src", torch.float32, 2)
+        _check(q_out, "q_out", None, 2)
+        d, G = k_store.head_dim, k_store.n_kv_heads
+        n = layout.n_rows
+        shared = v_store is k_store
+        v_plane = k_store.v if shared else v_store.k
+        if q_out.shape != (n, n_heads * d) or src.shape[0] < n or v_plane is None or \
+                src.shape[1] < max(q_col + n_heads * d, k_col + G * d, v_col + G * value_dim) or \
+                v_store.head_dim != value_dim or v_store.n_kv_heads != G or \
+                (q_gamma is not None and (q_gamma.numel() != d or k_gamma.numel() != d)) or \
+                (rot_dims and (freq is None or freq.numel() != rot_dims // 2)):
+            raise KernelError("qkv_norm_rope_append: shapes do not agree")
+        self._call("nb_qkv_norm_rope_append", _ptr(src), src.shape[1], q_col, k_col, v_col,
+                   _ptr(q_gamma), _ptr(k_gamma), float(eps), _ptr(freq), int(rot_dims),
+                   float(amplitude), _ptr(layout.row_slot), _ptr(layout.row_pos), _ptr(q_out),
+                   dtype_code(q_out.dtype), _ptr(k_store.k), _ptr(v_plane),
+                   dtype_code(k_store.k.dtype), _ptr(k_store.block_table),
+                   k_store.block_table.shape[1], _ptr(v_store.block_table),
+                   v_store.block_table.shape[1], k_store.page, n_heads, G, d, value_dim,
+                   1 if write else 0, n, self._stream())
+
+    def attention_masked(self, q, layout, k_store, v_store, n_heads, sink, out, scale, softcap=0.0,
+                         window=0, keep_first=0, chunk=0, gate=None, gate_col=0):
+        """Attention of the packed rows over ``k_store`` / ``v_store`` (as in
+        :meth:`attention_capped`) where position ``i`` sees ``j <= i`` with ``i - j < window`` or
+        ``j < keep_first`` (``window`` > 0), and only ``j`` of its own block of ``chunk`` positions
+        (``chunk`` > 0).  ``gate``: fp32 rows with a logit per head at columns ``gate_col ..``;
+        head ``h``'s result is multiplied by ``sigmoid`` of it."""
+        _check(q, "q", None, 2)
+        _check(out, "out", None, 2)
+        n, d, dv = layout.n_rows, k_store.head_dim, v_store.head_dim
+        shared = v_store is k_store
+        if q.shape != (n, n_heads * d) or out.shape != (n, n_heads * dv) or \
+                k_store.n_kv_heads != v_store.n_kv_heads or k_store.k.dtype != v_store.k.dtype or \
+                (shared and k_store.v is None):
+            raise KernelError("attention_masked: shapes do not agree")
+        if sink is not None:
+            _check(sink, "sink", torch.float32, 1)
+            if sink.numel() != n_heads:
+                raise KernelError("attention_masked: one sink per head")
+        if gate is not None:
+            _check(gate, "gate", torch.float32, 2)
+            if gate.shape[0] < n or gate.shape[1] < gate_col + n_heads:
+                raise KernelError("attention_masked: gate columns do not fit")
+        v_plane = k_store.v if shared else v_store.k
+        self._call("nb_attention_masked", _ptr(q), dtype_code(q.dtype), _ptr(layout.row_slot),
+                   _ptr(layout.row_pos), _ptr(k_store.k), _ptr(k_store.block_table),
+                   k_store.block_table.shape[1], _ptr(v_plane), _ptr(v_store.block_table),
+                   v_store.block_table.shape[1], dtype_code(k_store.k.dtype), k_store.page, n_heads,
+                   k_store.n_kv_heads, d, dv, _ptr(sink), _ptr(out), dtype_code(out.dtype),
+                   float(scale), float(softcap or 0.0), int(window), int(keep_first), int(chunk),
+                   _ptr(gate), gate.shape[1] if gate is not None else 0, int(gate_col), n,
+                   self._stream())
+
     def pool_blocks(self, layout, kv, blocks, pool):
         """For every row that completes a block of ``pool`` tokens: the means of the block's keys
         and values in ``kv`` into entry ``pos // pool`` of the paged store ``blocks``."""
@@ -918,15 +1013,16 @@ class CudaBackend:
                    float(next_eps), _ptr(out_next),
                    dtype_code(out_next.dtype) if out_next is not None else 0, n, d, self._stream())
 
-    def glu_rows(self, x, gate_col, up_col, act, out):
-        """``out[r, i] = act(x[r, gate_col + i]) * x[r, up_col + i]`` for fp32 rows ``x``."""
+    def glu_rows(self, x, gate_col, up_col, act, out, act_param=0.0):
+        """``out[r, i] = act(x[r, gate_col + i]) * x[r, up_col + i]`` for fp32 rows ``x`` (or the
+        combiner of ``ACT_SWISH_CLAMP`` with its bound ``act_param``)."""
         _check(x, "x", torch.float32, 2)
         _check(out, "out", None, 2)
         n, d = out.shape
         if x.shape[0] < n or x.shape[1] < max(gate_col, up_col) + d:
             raise KernelError("glu_rows: shapes do not agree")
-        self._call("nb_glu_rows", _ptr(x), x.shape[1], gate_col, up_col, int(act), _ptr(out),
-                   dtype_code(out.dtype), n, d, self._stream())
+        self._call("nb_glu_rows", _ptr(x), x.shape[1], gate_col, up_col, int(act), float(act_param),
+                   _ptr(out), dtype_code(out.dtype), n, d, self._stream())
 
     def cast_cols(self, x, out, out_col):
         """``out[:, out_col : out_col + d] = x`` (fp32 rows into columns of rows of another type)."""
@@ -951,6 +1047,28 @@ class CudaBackend:
         self._call("nb_moe_route", _ptr(logits), logits.shape[1], col, _ptr(layout.row_slot), n,
                    n_experts, top, 1 if renormalize else 0, _ptr(idx), _ptr(weight), self._stream())
 
+    def moe_route_sigmoid(self, logits, col, bias, n_experts, top, n_groups, keep_groups, group_top,
+                          renormalize, norm_eps, out_scale, layout, idx, weight):
+        """Per row: ``s = sigmoid(logits)``; choice scores ``s + bias`` (``bias`` may be ``None``);
+        with ``n_groups`` > 1 only experts of the ``keep_groups`` groups of neighbours with the
+        largest sums of their ``group_top`` best choice scores can be chosen; the ``top`` best
+        into ``idx``; ``weight`` = their ``s``, over ``(sum + norm_eps)`` if ``renormalize``,
+        times ``out_scale``."""
+        _check(logits, "logits", torch.float32, 2)
+        _check(idx, "idx", torch.int32, 2)
+        _check(weight, "weight", torch.float32, 2)
+        if bias is not None:
+            _check(bias, "bias", torch.float32, 1)
+            if bias.numel() != n_experts:
+                raise KernelError("moe_route_sigmoid: one bias per expert")
+        n = layout.n_rows
+        if logits.shape[0] < n or idx.shape != (n, top) or weight.shape != (n, top):
+            raise KernelError("moe_route_sigmoid: shapes do not agree")
+        self._call("nb_moe_route_sigmoid", _ptr(logits), logits.shape[1], col, _ptr(bias),
+                   _ptr(layout.row_slot), n, n_experts, top, int(n_groups), int(keep_groups),
+                   int(group_top), 1 if renormalize else 0, float(norm_eps), float(out_scale),
+                   _ptr(idx), _ptr(weight), self._stream())
+
     def moe_group(self, idx, n_experts, offsets, order, place):
         """Group the (row, choice) pairs of ``idx`` by expert: ``offsets`` ``[n_experts + 1]``,
         ``order`` (place -> pair) and ``place`` (pair -> place, -1 for none), all int32."""
@@ -962,10 +1080,11 @@ class CudaBackend:
         self._call("nb_moe_group", _ptr(idx), n_pairs, n_experts, _ptr(offsets), _ptr(order),
                    _ptr(place), self._stream())
 
-    def moe_linear(self, x, order, row_div, offsets, w, w2, out, act=ACT_NONE):
+    def moe_linear(self, x, order, row_div, offsets, w, w2, out, act=ACT_NONE, act_param=0.0):
         """A product per expert over its group: ``out[place] = x[row(place)] @ w[e].T``, or
         ``act(x @ w[e].T) * (x @ w2[e].T)`` with ``w2``; ``row(place) = order[place] // row_div``
-        with ``order``, else ``place``.  ``w``, ``w2``: ``[n_experts, N, K]``."""
+        with ``order``, else ``place``.  ``w``, ``w2``: ``[n_experts, N, K]``.  ``act_param``: the
+        number of a combiner that takes one (``ACT_SWISH_CLAMP``'s bound)."""
         _check(x, "x", None, 2)
         _check(w, "w", None, 3)
         _check(out, "out", None, 2)
@@ -990,18 +1109,19 @@ class CudaBackend:
                            n_experts, _ptr(xs), n_places, K, self._stream())
             self._call("nb_moe_gemm_tc", _ptr(xs), xs.shape[0], _ptr(offsets), n_experts, n_places,
                        _ptr(w), _ptr(w2), _ptr(out), dtype_code(out.dtype), out.shape[1], N, K, act,
-                       self._stream())
+                       float(act_param), self._stream())
             return
         if self.use_mma and out.dtype in (torch.bfloat16, torch.float32) \
                 and self.lib.nb_moe_gemm_mma_supported(dtype_code(x.dtype), dtype_code(w.dtype),
                                                        x.shape[1], K):
             self._call("nb_moe_gemm_mma", _ptr(x), x.shape[1], _ptr(order), row_div, _ptr(offsets),
                        n_experts, out.shape[0], _ptr(w), _ptr(w2), _ptr(out), dtype_code(out.dtype),
-                       out.shape[1], N, K, act, self._stream())
+                       out.shape[1], N, K, act, float(act_param), self._stream())
             return
         self._call("nb_moe_gemm", _ptr(x), dtype_code(x.dtype), x.shape[1], _ptr(order), row_div,
                    _ptr(offsets), n_experts, out.shape[0], _ptr(w), _ptr(w2), dtype_code(w.dtype),
-                   _ptr(out), dtype_code(out.dtype), out.shape[1], N, K, act, self._stream())
+                   _ptr(out), dtype_code(out.dtype), out.shape[1], N, K, act, float(act_param),
+                   self._stream())
 
     def moe_combine(self, y, place, weight, residual):
         """``residual[r] += sum_k weight[r, k] * y[place[r, k]]`` (fp32, ``k`` in order)."""

@@ -106,6 +106,90 @@ NB_EXPORT int nb_embed_pos(const int* tokens, const int* pos, const void* wte, c
 }
 
 // ---------------------------------------------------------------------------------
+// x[r] = scale * wte[token[r]] + pair[bucket(r)], fp32 result: a second table indexed by a hash
+// of (previous token, token):  bucket = (prev * mul_prev + token * mul_cur) mod n_buckets, and
+// row n_buckets (the table's last) for a sequence's first token.  The previous token of a row is
+// the row before it in the step, or, for the first row of a continued sequence, what the
+// sequence's state row holds (`last`, one float per slot: token ids are exact there).
+// `last` is only read here; nb_last_token writes it once every row has been embedded.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_hashed_kernel(const int* tokens, const int* pos, const int* row_slot,
+                                    const T* __restrict__ wte, const T* __restrict__ pair,
+                                    const float* last, int last_stride, float* out, int d,
+                                    float scale, int mul_prev, int mul_cur, int n_buckets) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  const int r = blockIdx.x;
+  const int tok = tokens[r];
+  float* o = out + (size_t)r * d;
+  const int slot = row_slot[r];
+  if (tok < 0 || slot < 0) {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = 0.0f;
+    return;
+  }
+  const int p = pos[r];
+  long long bucket = n_buckets;
+  if (p > 0) {
+    int prev;
+    if (r > 0 && row_slot[r - 1] == slot && pos[r - 1] == p - 1) prev = tokens[r - 1];
+    else prev = (int)last[(size_t)slot * last_stride];
+    bucket = ((long long)prev * mul_prev + (long long)tok * mul_cur) % n_buckets;
+    if (bucket < 0) bucket += n_buckets;
+  }
+  const T* e = wte + (size_t)tok * d;
+  const T* b = pair + (size_t)bucket * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x)
+    o[i] = nb_to_f32(e[i]) * scale + nb_to_f32(b[i]);
+}
+
+// last[slot] = token of the sequence's last row in this step (a row whose successor is not the
+// same sequence's next token).
+__global__ void last_token_kernel(const int* tokens, const int* pos, const int* row_slot,
+                                  float* last, int last_stride, int n_rows) {
+  nb_grid_dependency_wait();
+  nb_launch_dependents();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n_rows) return;
+  const int slot = row_slot[r];
+  if (slot < 0 || tokens[r] < 0) return;
+  const bool more = r + 1 < n_rows && row_slot[r + 1] == slot && pos[r + 1] == pos[r] + 1;
+  if (!more) last[(size_t)slot * last_stride] = (float)tokens[r];
+}
+
+NB_EXPORT int nb_embed_hashed(const int* tokens, const int* pos, const int* row_slot, const void* wte,
+                              const void* pair, int table_dtype, const float* last, int last_stride,
+                              float* out, int n_rows, int d, float scale, int mul_prev, int mul_cur,
+                              int n_buckets, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && d > 0 && n_buckets > 0 && last != nullptr, NB_ERR_BAD_ARG,
+             "embed_hashed: bad sizes rows=%d d=%d buckets=%d", n_rows, d, n_buckets);
+  const int threads = d >= 256 ? 256 : (d >= 128 ? 128 : 64);
+  if (table_dtype == NB_F32)
+    NB_CUDA(nb_launch(embed_hashed_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, tokens, pos,
+                      row_slot, (const float*)wte, (const float*)pair, last, last_stride, out, d,
+                      scale, mul_prev, mul_cur, n_buckets));
+  else if (table_dtype == NB_BF16)
+    NB_CUDA(nb_launch(embed_hashed_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream,
+                      tokens, pos, row_slot, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)pair,
+                      last, last_stride, out, d, scale, mul_prev, mul_cur, n_buckets));
+  else
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "embed_hashed: unknown table dtype %d", table_dtype);
+  NB_CHECK_LAUNCH("embed_hashed");
+  return 0;
+}
+
+NB_EXPORT int nb_last_token(const int* tokens, const int* pos, const int* row_slot, float* last,
+                            int last_stride, int n_rows, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  NB_REQUIRE(n_rows > 0 && last != nullptr && last_stride > 0, NB_ERR_BAD_ARG, "last_token: bad sizes");
+  NB_CUDA(nb_launch(last_token_kernel, dim3((n_rows + 127) / 128), dim3(128), 0, stream, tokens, pos,
+                    row_slot, last, last_stride, n_rows));
+  NB_CHECK_LAUNCH("last_token");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
 // LayerNorm of fp32 rows (src/ops.rs:32-40): mean, biased variance of (x - mean), both in
 // fp32 and in two passes; y = (x - mean) / sqrt(var + eps) * gamma + beta.
 // `rows` (optional) selects the source row of each output row; a negative entry gives zeros.
@@ -347,7 +431,7 @@ NB_EXPORT int nb_rmsnorm(const float* x, int x_stride, int x_col, const int* row
 // ---------------------------------------------------------------------------------
 constexpr int RA_MAX = 8;
 
-template <typename TOut>
+template <typename TOut, bool CENTER>
 __global__ void rms_add_kernel(const float* y, const float* __restrict__ gamma, float eps, float* x,
                                const float* __restrict__ next_gamma, float next_eps,
                                TOut* out_next, TOut* out_cast, int d) {
@@ -363,7 +447,18 @@ __global__ void rms_add_kernel(const float* y, const float* __restrict__ gamma, 
   for (int a = 0; a < RA_MAX; ++a) {
     const int i = threadIdx.x + a * blockDim.x;
     v[a] = i < d ? yr[i] : 0.0f;
-    ss = fmaf(v[a], v[a], ss);
+    if (!CENTER) ss = fmaf(v[a], v[a], ss);
+  }
+  if (CENTER) {
+    float s1 = 0.0f;
+#pragma unroll
+    for (int a = 0; a < RA_MAX; ++a) s1 += v[a];
+    const float mean = nb_block_sum(s1, red) / (float)d;
+#pragma unroll
+    for (int a = 0; a < RA_MAX; ++a) {
+      v[a] = threadIdx.x + a * blockDim.x < d ? v[a] - mean : 0.0f;
+      ss = fmaf(v[a], v[a], ss);
+    }
   }
   ss = nb_block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)d + eps);
@@ -378,9 +473,20 @@ __global__ void rms_add_kernel(const float* y, const float* __restrict__ gamma, 
     } else {
       v[a] = 0.0f;
     }
-    s2 = fmaf(v[a], v[a], s2);
+    if (!CENTER) s2 = fmaf(v[a], v[a], s2);
   }
   if (out_next == nullptr) return;
+  if (CENTER) {
+    float s1 = 0.0f;
+#pragma unroll
+    for (int a = 0; a < RA_MAX; ++a) s1 += v[a];
+    const float mean = nb_block_sum(s1, red) / (float)d;
+#pragma unroll
+    for (int a = 0; a < RA_MAX; ++a) {
+      v[a] = threadIdx.x + a * blockDim.x < d ? v[a] - mean : 0.0f;
+      s2 = fmaf(v[a], v[a], s2);
+    }
+  }
   s2 = nb_block_sum(s2, red);
   const float inv2 = 1.0f / sqrtf(s2 / (float)d + next_eps);
 #pragma unroll
@@ -410,7 +516,7 @@ __device__ __forceinline__ void nb_store4<__nv_bfloat16>(__nv_bfloat16* p, float
   *reinterpret_cast<uint2*>(p) = u;
 }
 
-template <typename TOut, int NV>
+template <typename TOut, int NV, bool CENTER>
 __global__ void __launch_bounds__(128)
 rms_add_warp_kernel(const float* y, const float* __restrict__ gamma, float eps, float* x,
                     const float* __restrict__ next_gamma, float next_eps, TOut* out_next,
@@ -430,6 +536,14 @@ rms_add_warp_kernel(const float* y, const float* __restrict__ gamma, float eps, 
     v[j] = yr[j * 32 + lane];
     xv[j] = xr[j * 32 + lane];
   }
+  if (CENTER) {
+    float s1 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) s1 += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    const float mean = nb_warp_sum(s1) / (float)d;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) { v[j].x -= mean; v[j].y -= mean; v[j].z -= mean; v[j].w -= mean; }
+  }
 #pragma unroll
   for (int j = 0; j < NV; ++j)
     ss = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, ss))));
@@ -446,9 +560,21 @@ rms_add_warp_kernel(const float* y, const float* __restrict__ gamma, float eps, 
     xr[j * 32 + lane] = v[j];
     if (out_cast != nullptr)
       nb_store4<TOut>(out_cast + (size_t)r * d + (j * 32 + lane) * 4, v[j].x, v[j].y, v[j].z, v[j].w);
-    s2 = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, s2))));
+    if (!CENTER)
+      s2 = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, s2))));
   }
   if (out_next == nullptr) return;
+  if (CENTER) {
+    float s1 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) s1 += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    const float mean = nb_warp_sum(s1) / (float)d;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      v[j].x -= mean; v[j].y -= mean; v[j].z -= mean; v[j].w -= mean;
+      s2 = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, s2))));
+    }
+  }
   s2 = nb_warp_sum(s2);
   const float inv2 = 1.0f / sqrtf(s2 / (float)d + next_eps);
   const float4* n4 = reinterpret_cast<const float4*>(next_gamma);
@@ -460,14 +586,14 @@ rms_add_warp_kernel(const float* y, const float* __restrict__ gamma, float eps, 
   }
 }
 
-template <typename TOut>
+template <typename TOut, bool CENTER>
 static int rms_add_warp(int nv, cudaStream_t stream, const float* y, const float* gamma, float eps,
                         float* x, const float* next_gamma, float next_eps, void* out_next,
                         void* out_cast, int d, int n_rows) {
   const dim3 grid((n_rows + 3) / 4), block(128);
 #define NB_RW(NV_)                                                                              \
   case NV_:                                                                                     \
-    NB_CUDA(nb_launch(rms_add_warp_kernel<TOut, NV_>, grid, block, 0, stream, y, gamma, eps, x, \
+    NB_CUDA(nb_launch(rms_add_warp_kernel<TOut, NV_, CENTER>, grid, block, 0, stream, y, gamma, eps, x, \
                       next_gamma, next_eps, (TOut*)out_next, (TOut*)out_cast, d, n_rows));      \
     break;
   switch (nv) {
@@ -479,42 +605,60 @@ static int rms_add_warp(int nv, cudaStream_t stream, const float* y, const float
   return 0;
 }
 
-NB_EXPORT int nb_rms_add(const float* y, const float* gamma, float eps, float* x,
+template <bool CENTER>
+static int norm_add_impl(const float* y, const float* gamma, float eps, float* x,
                          const float* next_gamma, float next_eps, void* out_next, void* out_cast,
                          int out_dtype, int n_rows, int d, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   NB_REQUIRE(n_rows > 0 && d > 0 && d <= RA_MAX * 1024, NB_ERR_BAD_ARG,
-             "rms_add: bad sizes rows=%d d=%d", n_rows, d);
+             "norm_add: bad sizes rows=%d d=%d", n_rows, d);
   NB_REQUIRE(gamma != nullptr && (out_next == nullptr || next_gamma != nullptr), NB_ERR_BAD_ARG,
-             "rms_add: a norm without its weight");
+             "norm_add: a norm without its weight");
   NB_REQUIRE(out_dtype == NB_F32 || out_dtype == NB_BF16, NB_ERR_BAD_ARG,
-             "rms_add: unknown output dtype %d", out_dtype);
+             "norm_add: unknown output dtype %d", out_dtype);
   // many rows of a width that a warp holds in registers: a warp per row
   const bool aligned = (((uintptr_t)y | (uintptr_t)x | (uintptr_t)gamma | (uintptr_t)next_gamma |
                          (uintptr_t)out_next | (uintptr_t)out_cast) & 15) == 0;
   if (d % 128 == 0 && d <= RW_MAX * 128 && n_rows >= 64 && aligned) {
     const int rc = out_dtype == NB_F32
-                       ? rms_add_warp<float>(d / 128, stream, y, gamma, eps, x, next_gamma, next_eps,
+                       ? rms_add_warp<float, CENTER>(d / 128, stream, y, gamma, eps, x, next_gamma, next_eps,
                                              out_next, out_cast, d, n_rows)
-                       : rms_add_warp<__nv_bfloat16>(d / 128, stream, y, gamma, eps, x, next_gamma,
+                       : rms_add_warp<__nv_bfloat16, CENTER>(d / 128, stream, y, gamma, eps, x, next_gamma,
                                                      next_eps, out_next, out_cast, d, n_rows);
     if (rc != 0) return rc;
-    NB_CHECK_LAUNCH("rms_add");
+    NB_CHECK_LAUNCH("norm_add");
     return 0;
   }
   int threads = 64;
   while (threads < 1024 && threads * (d > 2048 ? RA_MAX : 4) < d) threads *= 2;
   if (out_dtype == NB_F32)
-    NB_CUDA(nb_launch(rms_add_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, y, gamma, eps,
+    NB_CUDA(nb_launch(rms_add_kernel<float, CENTER>, dim3(n_rows), dim3(threads), 0, stream, y, gamma, eps,
                       x, next_gamma, next_eps, (float*)out_next, (float*)out_cast, d));
   else if (out_dtype == NB_BF16)
-    NB_CUDA(nb_launch(rms_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, y,
+    NB_CUDA(nb_launch(rms_add_kernel<__nv_bfloat16, CENTER>, dim3(n_rows), dim3(threads), 0, stream, y,
                       gamma, eps, x, next_gamma, next_eps, (__nv_bfloat16*)out_next,
                       (__nv_bfloat16*)out_cast, d));
   else
-    NB_REQUIRE(false, NB_ERR_BAD_ARG, "rms_add: unknown output dtype %d", out_dtype);
-  NB_CHECK_LAUNCH("rms_add");
+    NB_REQUIRE(false, NB_ERR_BAD_ARG, "norm_add: unknown output dtype %d", out_dtype);
+  NB_CHECK_LAUNCH("norm_add");
   return 0;
+}
+
+NB_EXPORT int nb_rms_add(const float* y, const float* gamma, float eps, float* x,
+                         const float* next_gamma, float next_eps, void* out_next, void* out_cast,
+                         int out_dtype, int n_rows, int d, cudaStream_t stream) {
+  return norm_add_impl<false>(y, gamma, eps, x, next_gamma, next_eps, out_next, out_cast, out_dtype,
+                              n_rows, d, stream);
+}
+
+// The same pass with both norms centred (a layer norm with a weight and no shift):
+//   x[r] += (y[r] - mean) / sqrt(var + eps) * gamma;  out_next[r] = the same norm of x[r] with
+//   next_gamma / next_eps;  out_cast[r] = x[r].  The variance is the mean squared deviation.
+NB_EXPORT int nb_ln_add(const float* y, const float* gamma, float eps, float* x,
+                        const float* next_gamma, float next_eps, void* out_next, void* out_cast,
+                        int out_dtype, int n_rows, int d, cudaStream_t stream) {
+  return norm_add_impl<true>(y, gamma, eps, x, next_gamma, next_eps, out_next, out_cast, out_dtype,
+                             n_rows, d, stream);
 }
 
 // ---------------------------------------------------------------------------------
@@ -614,12 +758,12 @@ NB_EXPORT int nb_gather_mul(const float* g, const void* table, int table_dtype, 
 }
 
 // ---------------------------------------------------------------------------------
-// out[r, i] = act(x[r, gate_col + i]) * x[r, up_col + i]: the gated half of a feed-forward whose
+// out[r, i] = act(x[r, gate_col + i]) * x[r, up_col + i] (nb_gate_up): the gated half of a feed-forward whose
 // two first products come side by side in one fp32 row.
 // ---------------------------------------------------------------------------------
 template <typename TOut>
 __global__ void glu_rows_kernel(const float* x, int x_stride, int gate_col, int up_col, int act,
-                                TOut* out, int d, size_t total) {
+                                float act_param, TOut* out, int d, size_t total) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
@@ -627,12 +771,13 @@ __global__ void glu_rows_kernel(const float* x, int x_stride, int gate_col, int 
     const size_t r = e / d;
     const int i = (int)(e - r * d);
     const float* row = x + r * x_stride;
-    out[e] = nb_from_f32<TOut>(nb_apply_act(row[gate_col + i], act) * row[up_col + i]);
+    out[e] = nb_from_f32<TOut>(nb_gate_up<false>(row[gate_col + i], row[up_col + i], act, act_param));
   }
 }
 
-NB_EXPORT int nb_glu_rows(const float* x, int x_stride, int gate_col, int up_col, int act, void* out,
-                          int out_dtype, int n_rows, int d, cudaStream_t stream) {
+NB_EXPORT int nb_glu_rows(const float* x, int x_stride, int gate_col, int up_col, int act,
+                          float act_param, void* out, int out_dtype, int n_rows, int d,
+                          cudaStream_t stream) {
   if (n_rows == 0 || d == 0) return 0;
   NB_REQUIRE(n_rows > 0 && d > 0 && gate_col >= 0 && up_col >= 0 && x_stride >= gate_col + d &&
                  x_stride >= up_col + d,
@@ -642,10 +787,10 @@ NB_EXPORT int nb_glu_rows(const float* x, int x_stride, int gate_col, int up_col
   const int blocks = (int)((total + 1023) / 1024 < 148 * 8 ? (total + 1023) / 1024 : 148 * 8);
   if (out_dtype == NB_F32)
     NB_CUDA(nb_launch(glu_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, x_stride,
-                      gate_col, up_col, act, (float*)out, d, total));
+                      gate_col, up_col, act, act_param, (float*)out, d, total));
   else if (out_dtype == NB_BF16)
     NB_CUDA(nb_launch(glu_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, x,
-                      x_stride, gate_col, up_col, act, (__nv_bfloat16*)out, d, total));
+                      x_stride, gate_col, up_col, act, act_param, (__nv_bfloat16*)out, d, total));
   else
     NB_REQUIRE(false, NB_ERR_BAD_ARG, "glu_rows: unknown output dtype %d", out_dtype);
   NB_CHECK_LAUNCH("glu_rows");

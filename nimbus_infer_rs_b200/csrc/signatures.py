@@ -52,10 +52,14 @@ SIGNATURES = {
     "nb_set_overlap": "i",
     "nb_get_overlap": "",
     "nb_embed_pos": "ppppipiifp",
+    "nb_embed_hashed": "pppppipipiifiiip",
+    "nb_last_token": "ppppiip",
+    "nb_ln_add": "ppfppfppiiip",
     "nb_rms_add": "ppfppfppiiip",
     "nb_act_rows": "piiippiiip",
     "nb_gather_mul": "ppippiiip",
     "nb_qk_norm_rope_append": "piiippfpifpppippipiiiiiiip",
+    "nb_qkv_norm_rope_append": "piiiippfpifpppippipipiiiiiiiip",
     "nb_pool_blocks": "pppppipppiiiiiiip",
     "nb_attention_pooled_mma": "piippppppipppiiiiippiifiiiip",
     "nb_attention_pooled": "pipppppipppiiiiiippifiiip",
@@ -63,11 +67,12 @@ SIGNATURES = {
     "nb_conv_act": "piippiipippippiiiip",
     "nb_conv_state_update": "piiipippiip",
     "nb_attention_capped": "pippppippiiiiiiippiffip",
+    "nb_attention_masked": "pippppippiiiiiiippiffiiipiiip",
     "nb_selective_scan_supported": "i",
     "nb_selective_scan": "ppiiipppppiipippiipiip",
     "nb_linear_attention_supported": "ii",
     "nb_linear_attention": "piiiiippippiiipip",
-    "nb_glu_rows": "piiiipiiip",
+    "nb_glu_rows": "piiiifpiiip",
     "nb_cast_cols": "ppiiiiip",
     "nb_rmsnorm_gated": "pppiipiiifp",
     "nb_rms_pair_add": "ppppffppfpiiip",
@@ -81,17 +86,18 @@ SIGNATURES = {
     "nb_attention_latent_mma_supported": "iii",
     "nb_attention_latent_mma": "pppppppiiiippfiiiiippp",
     "nb_moe_gemm_mma_supported": "iiii",
-    "nb_moe_gemm_mma": "pipipiipppiiiiip",
+    "nb_moe_gemm_mma": "pipipiipppiiiiifp",
     "nb_head_linear_mma_supported": "iiiiii",
     "nb_head_linear_mma": "piiippipiipiiiip",
     "nb_moe_gemm_tc_set_wait_budget": "l",
     "nb_moe_gemm_tc_supported": "iiiiii",
     "nb_moe_gather": "pipipipiip",
-    "nb_moe_gemm_tc": "pipiipppiiiiip",
+    "nb_moe_gemm_tc": "pipiipppiiiiifp",
     "nb_moe_route": "piipiiiippp",
+    "nb_moe_route_sigmoid": "piippiiiiiiiffppp",
     "nb_moe_group": "piipppp",
     "nb_moe_gemm_tiles": "ii",
-    "nb_moe_gemm": "piipipiippipiiiiip",
+    "nb_moe_gemm": "piipipiippipiiiiifp",
     "nb_moe_combine": "pippipip",
     "nb_kv_append": "piiiipppppiiiiip",
     "nb_advance_decode": "ppppip",

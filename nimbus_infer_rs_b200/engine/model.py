@@ -15,6 +15,8 @@ from ..parts.base import ParamSpec, bind_params, build_part, collect_param_specs
 from ..parts.embedding import LMHead, TokenEmbedding
 from .spec import ModelSpec
 
+EMBEDDING_ENTRY = -1     # the key of the embedding's state rows among the schedule entries
+
 PRECISIONS = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
               "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
 
@@ -60,7 +62,8 @@ class Model:
         spec.validate()
         self.spec = spec
         self.rt = runtime
-        self.embedding = TokenEmbedding(spec.vocab_size, spec.width, spec.embedding_scale)
+        self.embedding = TokenEmbedding(spec.vocab_size, spec.width, spec.embedding_scale) \
+            if spec.embedding is None else build_part("embedding", spec.embedding)
         self.position = build_part("position", spec.position)
         self.layers = [Layer(i, ls) for i, ls in enumerate(spec.layers)]
         final_norm = spec.final_norm
@@ -128,6 +131,7 @@ class Model:
     # ------------------------------------------------------------------ forward
     def forward_hidden(self, ctx) -> torch.Tensor:
         """The fp32 residual stream after the last scheduled layer, [rows, width]."""
+        ctx.state = ctx.cache.layer_state(EMBEDDING_ENTRY)
         x = self.embedding.forward(ctx, self.position)
         x0 = x
         if self.stream_input_before and min(self.stream_input_before) > 0:
@@ -167,6 +171,9 @@ class Model:
             s = layer.mixer.state_request()
             if s is not None:
                 st[entry] = s
+        s = self.embedding.state_request()
+        if s is not None:
+            st[EMBEDDING_ENTRY] = s
         return kv, st
 
     def extra_storage_requests(self):

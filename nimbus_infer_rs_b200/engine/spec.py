@@ -10,7 +10,8 @@ an arrangement in which both sublayers read one norm has no second norm (``norm_
 ``max_seq_len=None``: nothing in the model bounds a sequence; the cache's size does.
 ``stream_input`` with ``stream_input_before``: a part of the ``stream`` family (one set of
 parameters) that transforms the stream right before each of the named schedule entries, from
-the stream and the embedding's output.  ``logit_scale`` multiplies the logits.
+the stream and the embedding's output.  ``logit_scale`` multiplies the logits.  ``embedding``: a
+part of the ``embedding`` family in place of the plain token table.
 """
 from __future__ import annotations
 
@@ -47,6 +48,9 @@ class ModelSpec:
     schedule: tuple[int, ...] | None = None
     embedding_scale: float = 1.0      # multiplies the token embedding (not the tied head)
     logit_scale: float = 1.0          # multiplies the logits
+    # another way from tokens to the stream than the token table (``embedding`` family); its
+    # arguments must include ``vocab_size`` and ``width``
+    embedding: PartSpec | None = None
     stream_input: PartSpec | None = None
     stream_input_before: tuple[int, ...] = ()     # schedule entries (positions in the run order)
 

@@ -4,7 +4,7 @@ from .base import (INDEX, MATRIX, TABLE, VECTOR, Block, DeferredNorm, FeedForwar
 from .linear import Linear
 from .norm import LayerNorm, RMSNorm
 from .position import LearnedAbsolute, NoPosition
-from .embedding import LMHead, TokenEmbedding
+from .embedding import HashedPairEmbedding, LMHead, TokenEmbedding
 from .attention import CausalSelfAttention
 from .latent_attention import LatentAttention
 from .feed_forward import DenseMLP, GatedMLP
@@ -14,6 +14,7 @@ from .pooled_attention import PooledWindowAttention
 from .delta_rule import DeltaRule
 from .token_side import GatedTokenInput
 from .capped_attention import CappedAttention
+from .masked_attention import MaskedAttention
 from .selective_scan import SelectiveScan
 from .linear_attention import DecayedLinearAttention
 from .mixer_pair import NormedPair

@@ -23,6 +23,9 @@ family         interface
                after its sublayers (``x_act``: the stream's rows in the activation type)
 ``stream``     ``forward(ctx, x, x0) -> x'``: acts on the stream right before a schedule entry
                (``x0``: the embedding's output); the model lists which entries
+``embedding``  ``forward(ctx, position) -> x``: the fp32 stream from the step's tokens; the
+               default is the token table (plus a position table); may keep a state row per
+               sequence (``state_request()``, ``ctx.state`` while it runs)
 =============  ===========================================================================
 
 Every part lists its parameters with :meth:`Part.param_specs` (shape and role) and gets the
@@ -65,12 +68,14 @@ class KVRequest:
     and values, 1 for a mixer that keeps one vector per token and head (a latent that is key
     and value at once).  ``every`` > 1: one entry per ``every`` tokens of the sequence instead of
     one per token (a store of pooled blocks: entry ``b`` belongs to tokens ``b * every ..
-    b * every + every - 1`` and exists once the last of them is cached)."""
+    b * every + every - 1`` and exists once the last of them is cached).  ``keep_first`` (with a
+    window): the sequence's first ``keep_first`` tokens are read by every later token too."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
     planes: int = 2
     every: int = 1
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -197,6 +202,7 @@ class Block(Part):
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Part]]] = {
     "norm": {}, "position": {}, "mixer": {}, "ffn": {}, "block": {}, "side": {}, "stream": {},
+    "embedding": {},
 }
 
 

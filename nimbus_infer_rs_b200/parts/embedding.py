@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import MATRIX, TABLE, DeferredNorm, ParamSpec, Part
+from .base import MATRIX, TABLE, DeferredNorm, ParamSpec, Part, StateRequest, register_part
 
 
 class TokenEmbedding(Part):
@@ -22,10 +22,54 @@ class TokenEmbedding(Part):
     def param_specs(self):
         return {"table": ParamSpec((self.vocab_size, self.width), TABLE)}
 
+    def state_request(self):
+        """Fixed-size per-sequence storage of the embedding (``ctx.state`` while it runs)."""
+        return None
+
     def forward(self, ctx, position) -> torch.Tensor:
         lay = ctx.layout
         x = torch.empty((lay.n_rows, self.width), device=self.table.device, dtype=torch.float32)
         ctx.ops.embed_pos(lay.tokens, lay.row_pos, self.table, position.table, x, self.scale)
+        return x
+
+
+@register_part("embedding", "hashed_pair_embedding")
+class HashedPairEmbedding(TokenEmbedding):
+    """``x[i] = scale * table[token_i] + pair_table[b_i]``: beside the token's row, a row of a second
+    table chosen by a hash of the token and the one before it in its sequence,
+    ``b_i = (token_(i-1) * mul_prev + token_i * mul_cur) mod buckets``; a sequence's first token
+    takes the table's last row (row ``buckets``).
+
+    The token before a step's first one belongs to the sequence's state: one number per slot in
+    the sequence's state row (token ids are whole numbers below 2^24, exact in fp32), written
+    after the step's rows have been embedded."""
+    kind = "hashed_pair_embedding"
+
+    def __init__(self, vocab_size: int, width: int, buckets: int, mul_prev: int, mul_cur: int,
+                 scale: float = 1.0):
+        super().__init__(vocab_size, width, scale)
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        if self.buckets < 1:
+            raise ValueError("a hashed pair embedding needs at least one bucket")
+        if self.vocab_size >= 1 << 24:
+            raise ValueError("token ids beyond 2^24 do not fit the state row")
+        self.pair_table = None
+
+    def param_specs(self):
+        return {**super().param_specs(),
+                "pair_table": ParamSpec((self.buckets + 1, self.width), TABLE)}
+
+    def state_request(self):
+        return StateRequest(1)
+
+    def forward(self, ctx, position) -> torch.Tensor:
+        if position.table is not None:
+            raise ValueError("a hashed pair embedding does not add a position table")
+        lay = ctx.layout
+        x = torch.empty((lay.n_rows, self.width), device=self.table.device, dtype=torch.float32)
+        ctx.ops.embed_hashed(lay.tokens, lay.row_pos, lay.row_slot, self.table, self.pair_table,
+                             ctx.state, x, self.scale, self.mul_prev, self.mul_cur, self.buckets)
+        ctx.ops.last_token(lay.tokens, lay.row_pos, lay.row_slot, ctx.state, lay.n_rows)
         return x
 
 

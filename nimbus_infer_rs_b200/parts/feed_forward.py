@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from ..csrc.ops import ACTIVATIONS, GLU_ACTIVATIONS, ROW_ACTIVATIONS
+from ..csrc.ops import ACTIVATIONS, GLU_ACTIVATIONS, PARAM_ACTIVATIONS, ROW_ACTIVATIONS
 from .base import VECTOR, FeedForward, ParamSpec, register_part
 from .linear import Linear
 
@@ -56,7 +56,9 @@ class DenseMLP(FeedForward):
 @register_part("ffn", "gated_mlp")
 class GatedMLP(FeedForward):
     """``residual += Wdown (act(Wgate h) * (Wup h))`` without biases; ``activation`` is ``relu``,
-    ``silu``, ``gelu_tanh``, ``gelu_erf``, ``relu2`` or ``none``.
+    ``silu``, ``gelu_tanh``, ``gelu_erf``, ``relu2`` or ``none``; or ``swish_clamp`` with its bound
+    ``limit`` = L: ``g = min(Wgate h, L)``, ``u = clamp(Wup h, -L, L)``, and ``Wdown (g sigmoid(1.702
+    g) (u + 1))``.
 
     One product gives ``[Wgate h | Wup h]`` side by side in fp32; a row pass applies the
     activation to the first half, multiplies by the second (both unrounded) and hands the
@@ -64,11 +66,14 @@ class GatedMLP(FeedForward):
     graph_safe = True
     can_overwrite = True
 
-    def __init__(self, width: int, hidden: int, activation: str):
+    def __init__(self, width: int, hidden: int, activation: str, limit: float | None = None):
         if activation not in GLU_ACTIVATIONS:
             raise ValueError(f"unknown activation {activation!r} (have {sorted(GLU_ACTIVATIONS)})")
+        if (limit is not None) != (activation in PARAM_ACTIVATIONS):
+            raise ValueError(f"activation {activation!r} and limit={limit!r} do not go together")
         self.width, self.hidden = int(width), int(hidden)
         self.activation = activation
+        self.act_param = float(limit) if limit is not None else 0.0
         self.act_code = GLU_ACTIVATIONS[activation]
         # the two halves start on multiples of 8 columns (fp32 rows on 32-byte boundaries)
         self.half = -(-self.hidden // 8) * 8
@@ -81,7 +86,7 @@ class GatedMLP(FeedForward):
     def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
         both = self.fc(ctx, h, out_dtype=torch.float32)
         mid = torch.empty((both.shape[0], self.hidden), device=both.device, dtype=ctx.rt.act_dtype)
-        ctx.ops.glu_rows(both, 0, self.half, self.act_code, mid)
+        ctx.ops.glu_rows(both, 0, self.half, self.act_code, mid, self.act_param)
         if accumulate:
             self.proj(ctx, mid, residual=residual)
         else:

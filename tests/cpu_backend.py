@@ -25,6 +25,42 @@ class CpuBackend:
             x = x + wpe[pos[:n].long()].float()
         out.copy_(torch.where(valid[:, None], x, torch.zeros_like(x)))
 
+    def embed_hashed(self, tokens, pos, row_slot, wte, pair, last, out, scale, mul_prev, mul_cur,
+                     n_buckets):
+        for r in range(out.shape[0]):
+            tok, slot, p = int(tokens[r]), int(row_slot[r]), int(pos[r])
+            if tok < 0 or slot < 0:
+                out[r].zero_()
+                continue
+            bucket = n_buckets
+            if p > 0:
+                if r > 0 and int(row_slot[r - 1]) == slot and int(pos[r - 1]) == p - 1:
+                    prev = int(tokens[r - 1])
+                else:
+                    prev = int(last[slot, 0])
+                bucket = (prev * mul_prev + tok * mul_cur) % n_buckets
+            out[r] = wte[tok].float() * scale + pair[bucket].float()
+
+    def last_token(self, tokens, pos, row_slot, last, n_rows):
+        for r in range(n_rows):
+            slot = int(row_slot[r])
+            if slot < 0 or int(tokens[r]) < 0:
+                continue
+            more = r + 1 < n_rows and int(row_slot[r + 1]) == slot and int(pos[r + 1]) == int(pos[r]) + 1
+            if not more:
+                last[slot, 0] = float(int(tokens[r]))
+
+    def ln_add(self, y, gamma, eps, residual, next_gamma, next_eps, out_next, out_cast):
+        def unit(t, e):
+            c = t - t.mean(-1, keepdim=True)
+            return c / torch.sqrt((c * c).mean(-1, keepdim=True) + e)
+        n = residual.shape[0]
+        residual += unit(y[:n], eps) * gamma
+        if out_next is not None:
+            out_next.copy_((unit(residual, next_eps) * next_gamma).to(out_next.dtype))
+        if out_cast is not None:
+            out_cast.copy_(residual.to(out_cast.dtype))
+
     def layernorm(self, x, gamma, beta, eps, out, rows=None):
         n = out.shape[0]
         src = x[:n] if rows is None else x[rows[:n].long().clamp(min=0)]
@@ -112,6 +148,65 @@ class CpuBackend:
             if write:
                 self._entry(kv, kv.k, slot, pos)[:] = turn(kn, pos).to(kv.k.dtype)
                 self._entry(kv, kv.v, slot, pos)[:] = k.to(kv.v.dtype)
+
+    def qkv_norm_rope_append(self, src, q_col, k_col, v_col, q_gamma, k_gamma, eps, freq, rot_dims,
+                             amplitude, layout, k_store, v_store, n_heads, value_dim, q_out, write):
+        d, G = k_store.head_dim, k_store.n_kv_heads
+        half = rot_dims // 2
+
+        def turn(x, pos):
+            if not rot_dims:
+                return x
+            ang = (torch.tensor(float(pos), dtype=torch.float32) * freq).float()
+            c, s = torch.cos(ang) * amplitude, torch.sin(ang) * amplitude
+            u, v = x[:, :half], x[:, half:rot_dims]
+            return torch.cat([u * c - v * s, v * c + u * s, x[:, rot_dims:]], dim=-1)
+
+        for r in range(layout.n_rows):
+            slot = int(layout.row_slot[r])
+            if slot < 0:
+                q_out[r].zero_()
+                continue
+            pos = int(layout.row_pos[r])
+            q = src[r, q_col:q_col + n_heads * d].float().view(n_heads, d)
+            k = src[r, k_col:k_col + G * d].float().view(G, d)
+            if q_gamma is not None:
+                q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * q_gamma
+                k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps) * k_gamma
+            q_out[r] = turn(q, pos).reshape(-1).to(q_out.dtype)
+            if write:
+                self._entry(k_store, k_store.k, slot, pos)[:] = turn(k, pos).to(k_store.k.dtype)
+                vals = self._values_of(k_store, v_store)
+                v = src[r, v_col:v_col + G * value_dim].float().view(G, value_dim)
+                self._entry(v_store, vals, slot, pos)[:] = v.to(vals.dtype)
+
+    def attention_masked(self, q, layout, k_store, v_store, n_heads, sink, out, scale, softcap=0.0,
+                         window=0, keep_first=0, chunk=0, gate=None, gate_col=0):
+        d, dv, G = k_store.head_dim, v_store.head_dim, k_store.n_kv_heads
+        group = n_heads // G
+        for r in range(layout.n_rows):
+            slot = int(layout.row_slot[r])
+            if slot < 0:
+                out[r].zero_()
+                continue
+            pos = int(layout.row_pos[r])
+            seen = [j for j in range(pos + 1)
+                    if (not window or pos - j < window or j < keep_first)
+                    and (not chunk or j // chunk == pos // chunk)]
+            keys = torch.stack([self._entry(k_store, k_store.k, slot, j).float() for j in seen])
+            vals = torch.stack([self._entry(v_store, self._values_of(k_store, v_store), slot, j).float() for j in seen])
+            qr = q[r].float().view(n_heads, d)
+            for h in range(n_heads):
+                s = (keys[:, h // group] @ qr[h]) * scale
+                if softcap:
+                    s = softcap * torch.tanh(s / softcap)
+                m = s.max() if sink is None else torch.maximum(s.max(), sink[h])
+                e = torch.exp(s - m)
+                den = e.sum() + (torch.exp(sink[h] - m) if sink is not None else 0.0)
+                o = (e / den) @ vals[:, h // group]
+                if gate is not None:
+                    o = o * torch.sigmoid(gate[r, gate_col + h])
+                out[r, h * dv:(h + 1) * dv] = o.to(out.dtype)
 
     def pool_blocks(self, layout, kv, blocks, pool):
         for r in range(layout.n_rows):
@@ -322,10 +417,17 @@ class CpuBackend:
             u = residual / torch.sqrt((residual * residual).mean(-1, keepdim=True) + next_eps)
             out_next.copy_((u * next_gamma).to(out_next.dtype))
 
-    def glu_rows(self, x, gate_col, up_col, act, out):
+    @classmethod
+    def _gate_up(cls, gate, up, act, param):
+        if act == 8:
+            g = torch.clamp(gate, max=param)
+            return g * torch.sigmoid(1.702 * g) * (torch.clamp(up, -param, param) + 1.0)
+        return cls._act(gate, act) * up
+
+    def glu_rows(self, x, gate_col, up_col, act, out, act_param=0.0):
         n, d = out.shape
-        out.copy_((self._act(x[:n, gate_col:gate_col + d].float(), act)
-                   * x[:n, up_col:up_col + d].float()).to(out.dtype))
+        out.copy_(self._gate_up(x[:n, gate_col:gate_col + d].float(),
+                                x[:n, up_col:up_col + d].float(), act, act_param).to(out.dtype))
 
     def cast_cols(self, x, out, out_col):
         out[:, out_col:out_col + x.shape[1]] = x.to(out.dtype)
@@ -388,6 +490,28 @@ class CpuBackend:
         idx.copy_(torch.where(live, order.to(torch.int32), torch.full_like(idx, -1)))
         weight.copy_(torch.where(live, w, torch.zeros_like(w)))
 
+    def moe_route_sigmoid(self, logits, col, bias, n_experts, top, n_groups, keep_groups, group_top,
+                          renormalize, norm_eps, out_scale, layout, idx, weight):
+        n = layout.n_rows
+        s = torch.sigmoid(logits[:n, col:col + n_experts].float())
+        c = s + bias if bias is not None else s.clone()
+        if n_groups > 1 and keep_groups < n_groups:
+            per = n_experts // n_groups
+            gs = c.view(n, n_groups, per).topk(min(group_top, per), dim=-1).values.sum(-1)
+            kept = torch.sort(gs, dim=-1, descending=True, stable=True).indices[:, :keep_groups]
+            ok = torch.zeros((n, n_groups), dtype=torch.bool)
+            ok.scatter_(1, kept, True)
+            c = c.masked_fill(~ok[:, :, None].expand(n, n_groups, per).reshape(n, n_experts),
+                              -math.inf)
+        order = torch.sort(c, dim=-1, descending=True, stable=True).indices[:, :top]
+        w = torch.gather(s, 1, order)
+        if renormalize:
+            w = w / (w.sum(-1, keepdim=True) + norm_eps)
+        w = w * out_scale
+        live = (layout.row_slot[:n] >= 0)[:, None]
+        idx.copy_(torch.where(live, order.to(torch.int32), torch.full_like(idx, -1)))
+        weight.copy_(torch.where(live, w, torch.zeros_like(w)))
+
     def moe_group(self, idx, n_experts, offsets, order, place):
         flat = idx.reshape(-1)
         at = 0
@@ -400,7 +524,7 @@ class CpuBackend:
                 at += 1
         offsets[n_experts] = at
 
-    def moe_linear(self, x, order, row_div, offsets, w, w2, out, act=0):
+    def moe_linear(self, x, order, row_div, offsets, w, w2, out, act=0, act_param=0.0):
         n_experts = w.shape[0]
         for e in range(n_experts):
             for at in range(int(offsets[e]), int(offsets[e + 1])):
@@ -408,7 +532,9 @@ class CpuBackend:
                 v = w[e].float() @ x[row].float()
                 if w2 is None and act == 4:
                     v = torch.clamp(v, min=0.0) ** 2
-                if w2 is not None:
+                if w2 is not None and act == 8:
+                    v = self._gate_up(v, w2[e].float() @ x[row].float(), act, act_param)
+                elif w2 is not None:
                     if act == 3:
                         v = v * torch.sigmoid(v)
                     elif act == 1:

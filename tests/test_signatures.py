@@ -40,7 +40,7 @@ def test_declared_signatures_match_the_sources():
 # `__restrict__` in a kernel that can start before its predecessor has ended.
 CONSTANT_PARAMS = {"gamma", "beta", "bias", "W", "W2", "wte", "wpe", "q_gamma", "k_gamma", "next_gamma",
                    "freq", "params", "table", "a_bias", "norm_w", "sink", "decay", "dt_bias",
-                   "a_log", "d_skip", "gamma_a", "gamma_b"}
+                   "a_log", "d_skip", "gamma_a", "gamma_b", "pair"}
 
 
 def test_no_restrict_on_step_data_in_kernels_that_start_early():
