@@ -41,6 +41,24 @@ __device__ __forceinline__ float nb_sink_fix(float& l, float m, float sink_logit
   return fix;
 }
 
+// What a query at position `pos` sees among the keys j <= pos:
+//   window > 0:     j > pos - window, and besides those every j < keep_first (the sequence's
+//                   first tokens stay visible)
+//   block > 0:      j >= floor(pos / block) * block (only its own block of positions)
+//   neither:        every j
+struct NbMask {
+  int window;
+  int keep_first;
+  int block;
+  // the first key of the contiguous run that ends at `pos`
+  __host__ __device__ __forceinline__ int first_key(int pos) const {
+    if (block > 0) return (pos / block) * block;
+    return (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+  }
+  // whether the kept first tokens are a range of their own
+  __host__ __device__ __forceinline__ bool keeps() const { return window > 0 && keep_first > 0; }
+};
+
 template <typename T>
 struct Lane16;   // the 16 bytes a lane reads, as floats
 template <>

@@ -139,31 +139,45 @@ def expert(x, W, p, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ W[p + "down"].T
 
 
-def choose_experts(z, bias, top, groups, scale):
+def choose_experts(z, bias, top, groups, scale, follow=None, margin=0.0):
     """z: router logits [T, E].  Returns (indices [T, top], weights [T, top]).  Choice by
-    sigmoid(z) + bias among the experts of the best groups, weights from sigmoid(z) alone."""
+    sigmoid(z) + bias among the experts of the best groups, weights from sigmoid(z) alone.
+
+    ``follow`` [T, top]: what another implementation chose.  A row whose choice is a close call
+    (the last kept and the first left-out group, or the last chosen and the first left-out
+    expert, are within ``margin`` of each other) takes that choice instead of its own: rounding
+    may settle a close call either way."""
     T, E = z.shape
     s = torch.sigmoid(z)
     c = s + bias if bias is not None else s.clone()
+    close = torch.zeros(T, dtype=torch.bool)
     if groups:
         n, keep = groups["count"], groups["keep"]
         per = E // n
         by_group = c.view(T, n, per)
         score = by_group.sort(-1, descending=True).values[:, :, :2].sum(-1)
-        best = torch.sort(score, dim=-1, descending=True, stable=True).indices[:, :keep]
+        ranked = torch.sort(score, dim=-1, descending=True, stable=True)
+        if keep < n:
+            close |= (ranked.values[:, keep - 1] - ranked.values[:, keep]) < margin
         ok = torch.zeros(T, n, dtype=torch.bool)
-        ok.scatter_(1, best, True)
+        ok.scatter_(1, ranked.indices[:, :keep], True)
         c = c.masked_fill(~ok.repeat_interleave(per, dim=1), -math.inf)
-    idx = torch.sort(c, dim=-1, descending=True, stable=True).indices[:, :top]
+    ranked = torch.sort(c, dim=-1, descending=True, stable=True)
+    if top < E:
+        close |= (ranked.values[:, top - 1] - ranked.values[:, top]) < margin
+    idx = ranked.indices[:, :top]
+    if follow is not None:
+        idx = torch.where(close[:, None], follow.to(idx.dtype), idx)
     w = s.gather(1, idx)
     return idx, w / (w.sum(-1, keepdim=True) + 1e-20) * scale
 
 
-def routed_feed_forward(x, W, p, f):
+def routed_feed_forward(x, W, p, f, follow=None, margin=0.0):
     r = f["router"]
     bias = W.get(p + "correction")
     # the router reads the rows as the engine's product sees them in a 32-bit run: unrounded
-    idx, w = choose_experts(x @ W[p + "router"].T, bias, r["top"], r.get("groups"), r.get("scale", 1.0))
+    idx, w = choose_experts(x @ W[p + "router"].T, bias, r["top"], r.get("groups"), r.get("scale", 1.0),
+                            follow, margin)
     out = torch.zeros_like(x)
     for t in range(x.shape[0]):
         for e, a in zip(idx[t].tolist(), w[t]):
@@ -180,7 +194,7 @@ def owner(cfg, i):
     return i
 
 
-def layer_forward(x, W, cfg, i):
+def layer_forward(x, W, cfg, i, follow=None, margin=0.0):
     L, eps = cfg["layers"][i], cfg["norm"]["eps"]
     p = f"l{owner(cfg, i)}."
     y = attention_mixer(layer_norm(x, W[p + "norm1"], eps), W, p + "mix.", L["type"], L["mixer"], eps)
@@ -189,23 +203,29 @@ def layer_forward(x, W, cfg, i):
     if f:
         h = layer_norm(x, W[p + "norm2"], eps)
         y = dense_feed_forward(h, W, p + "mlp.") if f["kind"] == "dense" \
-            else routed_feed_forward(h, W, p + "mlp.", f)
+            else routed_feed_forward(h, W, p + "mlp.", f, follow, margin)
         x = x + layer_norm(y, W[p + "norm2b"], eps)
     return x
 
 
-def hidden_states(tokens, W, cfg):
-    """The stream after every layer run, [runs, T, D]."""
+def hidden_states(tokens, W, cfg, routed=None, margin=0.0):
+    """The stream after every layer run, [runs, T, D].  ``routed``: for every layer run with
+    routed experts, in order, the experts another implementation chose ([T, top]); close calls
+    follow it (:func:`choose_experts`)."""
     W = as_f64(W)
     x = embed(tokens, W, cfg)
     out = []
-    for i in range(len(cfg["layers"])):
-        x = layer_forward(x, W, cfg, i)
+    calls = iter(routed) if routed is not None else None
+    for i, L in enumerate(cfg["layers"]):
+        follow = None
+        if calls is not None and L.get("mlp") and L["mlp"]["kind"] == "moe":
+            follow = next(calls)[:len(tokens)]
+        x = layer_forward(x, W, cfg, i, follow, margin)
         out.append(x)
     return torch.stack(out)
 
 
-def logits(tokens, W, cfg):
+def logits(tokens, W, cfg, routed=None, margin=0.0):
     W = as_f64(W)
-    x = hidden_states(tokens, W, cfg)[-1]
+    x = hidden_states(tokens, W, cfg, routed, margin)[-1]
     return layer_norm(x, W["final.norm"], cfg["norm"]["eps"]) @ W["head"].T

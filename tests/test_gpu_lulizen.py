@@ -18,19 +18,18 @@ NAMES = ["A", "B", "C", "D"]
 # design.  Every sublayer's result is normed to unit size before it is added, so a rounding
 # error in a small result enters the stream at full size; the mechanisms alone are held to 2e-5
 # and 2e-2 in test_gpu_lulizen_kernels.py.
-TOL = {"float32": 1e-4, "bfloat16": 6e-2}
+TOL = {"float32": 1e-4, "bfloat16": 5e-2}
 
 
 def assert_close(got, ref, dtype, what=""):
-    """In 32-bit every row within the tolerance.  In bfloat16 one row in twenty-five (at least
-    one) may be over it (a token whose expert choice is a near tie takes another expert), none
-    over eight times it."""
+    """In 32-bit every row within the tolerance.  In bfloat16 one row in fifty (at least one) may
+    be over it, none over eight times it."""
     got, ref = got.detach().double().cpu(), ref.detach().double().cpu()
     assert got.shape == ref.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
     assert torch.isfinite(got).all(), f"{what}: non-finite values"
     rows = (got - ref).abs().reshape(got.shape[0], -1).max(dim=1).values / float(ref.abs().max())
     over = int((rows > TOL[dtype]).sum())
-    allowed = 0 if dtype == "float32" else max(1, got.shape[0] // 25)
+    allowed = 0 if dtype == "float32" else max(1, got.shape[0] // 50)
     assert over <= allowed and float(rows.max()) <= 8 * TOL[dtype], \
         f"{what}: {over} rows over {TOL[dtype]:.0e} (allowed {allowed}), worst {float(rows.max()):.3e} " \
         f"at row {int(rows.argmax())}"
@@ -52,8 +51,60 @@ def _tokens(vocab, n, seed):
     return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
 
 
-def _engine(models, name, dtype, cache_tokens=1024, **kw):
-    return Engine.load(models[name][0], dtype=dtype, cache_tokens=cache_tokens, **kw)
+# A router's choice between experts (or groups of experts) whose scores are closer than this is a
+# close call that rounding may settle either way; the plain implementation then follows the
+# engine (and insists on its own choice everywhere else).
+MARGIN = {"float32": 1e-4, "bfloat16": 0.05}
+
+
+class Routed:
+    """Notes what the router kernel chose, per slot, at every position of every layer run with
+    routed experts, for the steps that go through ``Engine.step``."""
+
+    def __init__(self, engine):
+        self.by_slot, self._calls = {}, []
+        ops, orig, step, alloc = engine.ops, engine.ops.moe_route_sigmoid, engine.step, engine.alloc_slot
+
+        def tapped(logits, col, bias, n_experts, top, *rest):
+            orig(logits, col, bias, n_experts, top, *rest)
+            self._calls.append(rest[-2].clone())            # idx
+
+        def stepped(entries):
+            ops.moe_route_sigmoid = tapped
+            try:
+                out = step(entries)
+            finally:
+                del ops.moe_route_sigmoid                    # the class's method is back
+            calls, self._calls = [c.cpu().long() for c in self._calls], []
+            at = 0
+            for e in entries:
+                n = len(e[1])
+                mine = [c[at:at + n] for c in calls]
+                old = self.by_slot.get(e[0])
+                self.by_slot[e[0]] = mine if old is None else [torch.cat([a, b]) for a, b in zip(old, mine)]
+                at += n
+            return out
+
+        def allocated():
+            slot = alloc()
+            self.by_slot.pop(slot, None)
+            return slot
+
+        engine.step, engine.alloc_slot = stepped, allocated
+
+
+def _engine(models, name, dtype, cache_tokens=1024, tap=True, **kw):
+    e = Engine.load(models[name][0], dtype=dtype, cache_tokens=cache_tokens, **kw)
+    if tap:
+        e.step_graphs = None               # every launch goes through Python: the tap sees it
+        e.routed = Routed(e)
+    return e
+
+
+def _plain(e, slot, toks, P, cfg, dtype):
+    """The plain logits of the sequence in ``slot``, close calls of the routers settled as the
+    engine settled them."""
+    return PL.logits(toks, P, cfg, routed=e.routed.by_slot.get(slot), margin=MARGIN[dtype])
 
 
 @pytest.mark.parametrize("name,dtype", _cases(NAMES))
@@ -64,7 +115,7 @@ def test_each_request_alone_and_whole(models, name, dtype):
         toks = _tokens(cfg["vocab"], n, 10 + i)
         s = e.alloc_slot()
         out = e.step([(s, toks, list(range(n)))])
-        assert_close(out, PL.logits(toks, P, cfg), dtype, f"{name} whole, {n} tokens")
+        assert_close(out, _plain(e, s, toks, P, cfg, dtype), dtype, f"{name} whole, {n} tokens")
         e.free_slot(s)
     e.check_errors()
 
@@ -91,7 +142,7 @@ def test_layer_by_layer_in_32_bit(models):
 def test_recorded_steps_give_what_plain_launches_give(models, name, dtype):
     """A step whose shape comes again is replayed from a CUDA graph: bit for bit the same."""
     _, cfg, _ = models[name]
-    e, plainly = _engine(models, name, dtype), _engine(models, name, dtype)
+    e, plainly = _engine(models, name, dtype, tap=False), _engine(models, name, dtype, tap=False)
     plainly.step_graphs = None
     for n in (1, 70, 1, 70, 1, 70):
         toks = _tokens(cfg["vocab"], n, n)
@@ -118,7 +169,7 @@ def test_last_tokens_one_by_one(models, name, dtype):
         for t in range(head, n):
             outs.append(e.step([(s, [toks[t]], [0])]))
         e.free_slot(s)
-        assert_close(torch.cat(outs), PL.logits(toks, P, cfg)[head - 1:], dtype, f"{name} from {head} of {n}")
+        assert_close(torch.cat(outs), _plain(e, s, toks, P, cfg, dtype)[head - 1:], dtype, f"{name} from {head} of {n}")
 
 
 @pytest.mark.parametrize("name,dtype", _cases(["A", "B", "D"]))
@@ -132,7 +183,7 @@ def test_portions_of_several_sizes(models, name, dtype):
     for size in (2, 61, 1, 2, 64, 3, 70):
         outs.append(e.step([(s, toks[at:at + size], list(range(size)))]))
         at += size
-    assert_close(torch.cat(outs), PL.logits(toks, P, cfg), dtype, f"{name} portions")
+    assert_close(torch.cat(outs), _plain(e, s, toks, P, cfg, dtype), dtype, f"{name} portions")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -161,7 +212,7 @@ def test_unequal_batches_on_slots_and_pages_used_again(models, name, dtype):
                 got[i].append(out[j])
             k += 1
         for i in range(3):
-            ref = PL.logits(seqs[i], P, cfg)
+            ref = _plain(e, slots[i], seqs[i], P, cfg, dtype)
             places = [0, heads[i] - 1] + list(range(heads[i], lens[i]))
             assert_close(torch.stack(got[i]), ref[places], dtype, f"{name} batch {turn} request {i}")
             e.free_slot(slots[i])
@@ -177,7 +228,7 @@ def test_long_decoding_from_the_first_token(models, name, dtype):
     toks = _tokens(cfg["vocab"], 250, 9)
     s = e.alloc_slot()
     outs = [e.step([(s, [t], [0])]) for t in toks]
-    assert_close(torch.cat(outs), PL.logits(toks, P, cfg), dtype, "250 tokens one by one")
+    assert_close(torch.cat(outs), _plain(e, s, toks, P, cfg, dtype), dtype, "250 tokens one by one")
 
 
 def test_greedy_generation_through_the_engines_loop(models):
@@ -199,7 +250,7 @@ def test_greedy_generation_through_the_engines_loop(models):
 
 
 def test_bfloat16_generation_runs_in_a_recorded_decode_session(models):
-    e = _engine(models, "B", "bfloat16", cache_tokens=8 * 64)
+    e = _engine(models, "B", "bfloat16", cache_tokens=8 * 64, tap=False)
     assert e.graph_safe
     prompts = [_tokens(320, n, n) for n in (9, 40)]
     a = e.generate(prompts, SamplingParams(max_new_tokens=20, temperature=0.0))
@@ -211,7 +262,7 @@ def test_bfloat16_generation_runs_in_a_recorded_decode_session(models):
 def test_a_row_that_stops_early_leaves_the_others_alone(models, dtype):
     """A sequence that meets a stop token becomes a padding row of the decode session; the others
     go on exactly as they do without the stop."""
-    e = _engine(models, "B", dtype, cache_tokens=8 * 64)
+    e = _engine(models, "B", dtype, cache_tokens=8 * 64, tap=False)
     prompts = [_tokens(320, n, 7 + n) for n in (12, 70, 3)]
     free = e.generate(prompts, SamplingParams(max_new_tokens=16, temperature=0.0))
     stop = free[0][4]
