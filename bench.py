@@ -20,7 +20,8 @@ events around exactly K captured steps), ``e2e`` = the same through the Python e
 * ``clocks`` and ``gpu_launches``.
 
 ``python bench.py --designs`` is another measurement with a line of its own (the default
-workload and its line stay as they are): the Runesun design (latent attention, routed experts)
+workload and its line stay as they are): with ``--design`` one of the other designs (Runesun,
+Rizitar, Pinozen, Lulizen) beside GPT-2 or the closest design; by default the Runesun design (latent attention, routed experts)
 beside GPT-2 at equal layer sizes (presets ``runesun-2k`` / ``gpt2-2k`` and ``runesun-1k`` /
 ``gpt2-1k``, random weights): decode steps at batch 8 and 64 and a 2 x 1024-token prefill, and
 per kind of kernel the time inside a plainly launched step with its bytes, flops and fraction of
@@ -292,7 +293,10 @@ def run_workload(engine, cfg, prompt_lens, n_new, hbm_gbs, windows=()):
 DESIGN_PAIRS = {"runesun": (("runesun-2k", "gpt2-2k"), ("runesun-1k", "gpt2-1k")),
                 "rizitar": (("rizitar-2k", "gpt2-2k"), ("rizitar-1k", "gpt2-1k")),
                 # beside the closest design of the library: recurrent layers among attention layers
-                "pinozen": (("pinozen-2k", "rizitar-2k"), ("pinozen-1k", "rizitar-1k"))}
+                "pinozen": (("pinozen-2k", "rizitar-2k"), ("pinozen-1k", "rizitar-1k")),
+                # beside the closest design of the library: sublayers between two norms, attention
+                # with normed and rotated queries and keys over a window, routed experts
+                "lulizen": (("lulizen-2k", "rizitar-2k"), ("lulizen-1k", "rizitar-1k"))}
 
 
 class OpTimer:
@@ -305,7 +309,8 @@ class OpTimer:
              "rms_add", "act_rows", "gather_mul", "qk_norm_rope_append", "pool_blocks",
              "attention_pooled", "delta_rule", "conv_rope_append", "conv_act", "attention_capped",
              "selective_scan", "linear_attention", "rmsnorm_gated", "rms_pair_add", "glu_rows",
-             "cast_cols")
+             "cast_cols", "embed_hashed", "last_token", "ln_add", "qkv_norm_rope_append",
+             "attention_masked", "moe_route_sigmoid")
 
     def __init__(self, ops):
         import torch
@@ -390,8 +395,31 @@ class OpTimer:
             return 4 * out.numel() + nb(out), 0
         if kind == "moe_combine":
             return nb(a[0]) + 2 * nb(a[3]), 0
-        if kind == "rms_add":
+        if kind in ("rms_add", "ln_add"):
             return nb(a[0], a[6], a[7]) + 2 * nb(a[3]), 0
+        if kind == "embed_hashed":
+            return a[6].numel() * (4 + 2 * a[3].element_size()), 0
+        if kind == "moe_route_sigmoid":
+            return nb(a[0]) + 2 * nb(a[12]), 0
+        if kind == "qkv_norm_rope_append":
+            lay, ks, vs, heads, q = a[10], a[11], a[12], a[13], a[15]
+            kv = ks.n_kv_heads * (ks.head_dim + vs.head_dim)
+            return lay.n_tokens * (4 * (heads * ks.head_dim + kv) + kv * ks.k.element_size()) + nb(q), 0
+        if kind == "attention_masked":
+            q, lay, ks, vs, heads, out = a[0], a[1], a[2], a[3], a[4], a[6]
+            window, keep, block = (list(a[9:12]) + [0, 0, 0])[:3] if len(a) > 9 else (
+                kw.get("window", 0), kw.get("keep_first", 0), kw.get("chunk", 0))
+            elt = ks.k.element_size()
+
+            def first(i):       # the first key of the run that ends at position i
+                return (i // block) * block if block else (max(0, i + 1 - window) if window else 0)
+            pairs = sum(i + 1 - first(i) + (min(keep, first(i)) if window else 0)
+                        for p, n in zip(lay.seq_pos0_host, lay.seq_lens) for i in range(p, p + n))
+            # every sequence's keys once (neighbouring rows share them), queries, outputs
+            keys = sum(p + n - first(p) + (min(keep, first(p)) if window else 0)
+                       for p, n in zip(lay.seq_pos0_host, lay.seq_lens))
+            return keys * ks.n_kv_heads * (ks.head_dim + vs.head_dim) * elt + nb(q, out), \
+                2 * pairs * heads * (ks.head_dim + vs.head_dim)
         if kind == "act_rows":
             return 4 * a[4].numel() + nb(a[4]), 0
         if kind == "gather_mul":

@@ -27,12 +27,13 @@ constexpr int ROUTE_MAX_PER_LANE = 32;   // n_experts <= 32 * this
 // The `top` largest of the lane-distributed values v (entry i of a lane is expert lane + 32 i;
 // NEG marks "none" or "taken"), of equal values the lower index: the k-th winner's index goes to
 // out_e[k] of every lane and its entry is marked taken.
-__device__ __forceinline__ void route_take_best(float (&v)[ROUTE_MAX_PER_LANE], int lane, float neg,
+template <int PL>
+__device__ __forceinline__ void route_take_best(float (&v)[PL], int lane, float neg,
                                                 float& best, int& best_e) {
   best = neg;
   best_e = 0x7fffffff;
 #pragma unroll
-  for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+  for (int i = 0; i < PL; ++i) {
     const int e = lane + 32 * i;
     if (v[i] > best) { best = v[i]; best_e = e; }     // ascending e within a lane: first wins
   }
@@ -43,7 +44,7 @@ __device__ __forceinline__ void route_take_best(float (&v)[ROUTE_MAX_PER_LANE], 
     if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
   }
 #pragma unroll
-  for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
+  for (int i = 0; i < PL; ++i)
     if (lane + 32 * i == best_e) v[i] = neg;
 }
 
@@ -106,6 +107,7 @@ __global__ void moe_route_kernel(const float* logits, int stride, int col, const
 // scores the lower group) can be chosen.  The `top` allowed experts with the largest choice
 // scores are chosen (of equal scores the lower index); their weights are their s (without the
 // bias), divided by (their sum + norm_eps) when `renormalize`, times `out_scale`.
+template <int PL>   // experts a lane holds: n_experts <= 32 * PL
 __global__ void moe_route_sigmoid_kernel(const float* logits, int stride, int col,
                                          const float* __restrict__ bias, const int* row_slot,
                                          int n_rows, int n_experts, int top, int n_groups,
@@ -124,9 +126,9 @@ __global__ void moe_route_sigmoid_kernel(const float* logits, int stride, int co
     return;
   }
   const float* z = logits + (size_t)r * stride + col;
-  float s[ROUTE_MAX_PER_LANE], c[ROUTE_MAX_PER_LANE];
+  float s[PL], c[PL];
 #pragma unroll
-  for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+  for (int i = 0; i < PL; ++i) {
     const int e = lane + 32 * i;
     s[i] = e < n_experts ? 1.0f / (1.0f + expf(-z[e])) : 0.0f;
     c[i] = e < n_experts ? s[i] + (bias != nullptr ? bias[e] : 0.0f) : -INFINITY;
@@ -135,13 +137,13 @@ __global__ void moe_route_sigmoid_kernel(const float* logits, int stride, int co
     // group scores: lane g (+ 32 j) owns group g; every group's `group_top` largest are taken
     // from a copy of the choice scores, one group after the other
     const int per = n_experts / n_groups;
-    float gs[ROUTE_MAX_PER_LANE];     // gs[j]: score of group lane + 32 j
+    float gs[PL];     // gs[j]: score of group lane + 32 j
 #pragma unroll
-    for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j) gs[j] = -INFINITY;
+    for (int j = 0; j < PL; ++j) gs[j] = -INFINITY;
     for (int g = 0; g < n_groups; ++g) {
-      float t[ROUTE_MAX_PER_LANE];
+      float t[PL];
 #pragma unroll
-      for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+      for (int i = 0; i < PL; ++i) {
         const int e = lane + 32 * i;
         t[i] = (e >= g * per && e < (g + 1) * per) ? c[i] : -INFINITY;
       }
@@ -153,7 +155,7 @@ __global__ void moe_route_sigmoid_kernel(const float* logits, int stride, int co
         total += best;
       }
 #pragma unroll
-      for (int j = 0; j < ROUTE_MAX_PER_LANE; ++j)
+      for (int j = 0; j < PL; ++j)
         if (lane + 32 * j == g) gs[j] = total;
     }
     // the kept groups, as a bit per group held by the lane that owns it
@@ -165,7 +167,7 @@ __global__ void moe_route_sigmoid_kernel(const float* logits, int stride, int co
       if (best_g != 0x7fffffff && (best_g & 31) == lane) kept_bits |= 1u << (best_g >> 5);
     }
 #pragma unroll
-    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+    for (int i = 0; i < PL; ++i) {
       const int e = lane + 32 * i;
       const int g = min(e, n_experts - 1) / per;        // every lane takes part in the shuffle
       const unsigned bits = __shfl_sync(0xffffffffu, kept_bits, g & 31);
@@ -179,7 +181,7 @@ __global__ void moe_route_sigmoid_kernel(const float* logits, int stride, int co
     route_take_best(c, lane, -INFINITY, best, best_e);
     float sv = 0.0f;
 #pragma unroll
-    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
+    for (int i = 0; i < PL; ++i)
       if (lane + 32 * i == best_e) sv = s[i];
     sv = nb_warp_sum(sv);             // one lane holds it, the others zero
     chosen_sum += sv;
@@ -370,9 +372,15 @@ NB_EXPORT int nb_moe_route_sigmoid(const float* logits, int stride, int col, con
                    group_top >= 1 && keep_groups * (n_experts / n_groups) >= top,
                NB_ERR_BAD_ARG, "moe_route_sigmoid: %d groups (keep %d, top %d of each) of %d experts, top=%d",
                n_groups, keep_groups, group_top, n_experts, top);
-  NB_CUDA(nb_launch(moe_route_sigmoid_kernel, dim3((n_rows + 3) / 4), dim3(128), 0, stream, logits,
-                    stride, col, bias, row_slot, n_rows, n_experts, top, n_groups, keep_groups,
-                    group_top, renormalize, norm_eps, out_scale, idx, weight));
+#define NB_RS(PL_)                                                                               \
+  NB_CUDA(nb_launch(moe_route_sigmoid_kernel<PL_>, dim3((n_rows + 3) / 4), dim3(128), 0, stream, \
+                    logits, stride, col, bias, row_slot, n_rows, n_experts, top, n_groups,       \
+                    keep_groups, group_top, renormalize, norm_eps, out_scale, idx, weight))
+  if (n_experts <= 32) NB_RS(1);
+  else if (n_experts <= 64) NB_RS(2);
+  else if (n_experts <= 256) NB_RS(8);
+  else NB_RS(ROUTE_MAX_PER_LANE);
+#undef NB_RS
   NB_CHECK_LAUNCH("moe_route_sigmoid");
   return 0;
 }
