@@ -29,7 +29,7 @@ class LayerNorm(Norm):
     def add_into(self, ctx, y, residual, then: "LayerNorm | None" = None, rounded: bool = False):
         """``residual += norm(y)`` for a sublayer's fp32 result ``y`` in one pass over the rows,
         which can also hand out ``then(residual)`` (the norm in front of the next sublayer) and,
-        with ``rounded``, the stream's rows in the activation type; the contract of
+        with ``rounded``, the stream's rows in the activation type; the interface of
         :meth:`RMSNorm.add_into`.  Only for norms without a shift."""
         if self.has_bias or (then is not None and getattr(then, "has_bias", True)):
             raise ValueError("add_into: only layer norms without a shift are added in one pass")
