@@ -41,15 +41,22 @@ __device__ __forceinline__ float nb_sink_fix(float& l, float m, float sink_logit
   return fix;
 }
 
-// What a query at position `pos` sees among the keys j <= pos:
+// Options of the masked attention kernels.  What a query at position `pos` sees among the keys
+// j <= pos:
 //   window > 0:     j > pos - window, and besides those every j < keep_first (the sequence's
 //                   first tokens stay visible)
 //   block > 0:      j >= floor(pos / block) * block (only its own block of positions)
 //   neither:        every j
-struct NbMask {
+//
+// gate (or null): fp32 rows with one logit per head at columns gate_col ..; head h's result of row
+// r is multiplied by sigmoid(gate[r * gate_stride + gate_col + h]) where the row's sum divides it.
+struct NbAttnOpts {
   int window;
   int keep_first;
   int block;
+  const float* gate;
+  int gate_stride;
+  int gate_col;
   // the first key of the contiguous run that ends at `pos`
   __host__ __device__ __forceinline__ int first_key(int pos) const {
     if (block > 0) return (pos / block) * block;
@@ -57,6 +64,11 @@ struct NbMask {
   }
   // whether the kept first tokens are a range of their own
   __host__ __device__ __forceinline__ bool keeps() const { return window > 0 && keep_first > 0; }
+  // the factor of head `head` of row `r`
+  __device__ __forceinline__ float gate_of(int r, int head) const {
+    return gate == nullptr ? 1.0f
+                           : 1.0f / (1.0f + expf(-gate[(size_t)r * gate_stride + gate_col + head]));
+  }
 };
 
 template <typename T>

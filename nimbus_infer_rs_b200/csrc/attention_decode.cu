@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(THREADS)
 attention_decode_kernel(const T* q, int q_stride, int q_col,
                         const int* row_slot, const int* row_pos,
                         NbPagedKV kv, int group, TOut* out, int out_stride,
-                        float scale, float softcap, const float* sink, NbMask mask, int n_splits, float* part_acc,
+                        float scale, float softcap, const float* sink, NbAttnOpts opt, int n_splits, float* part_acc,
                         float* part_ml, int* counters, int append,
                         int k_col, int v_col) {
   constexpr int EPL = Lane16<T>::N;           // elements per lane
@@ -70,15 +70,15 @@ attention_decode_kernel(const T* q, int q_stride, int q_col,
   }
   const int pos = row_pos[r];
   const int kv_len = pos + 1;
-  const int j_begin = mask.first_key(pos);
-  const int keep_first = mask.keeps() ? mask.keep_first : 0;
+  const int j_begin = opt.first_key(pos);
+  const int keep_first = opt.keeps() ? opt.keep_first : 0;
   const int first_page = j_begin / PAGE_TOKENS;
   const int n_pages = (kv_len + PAGE_TOKENS - 1) / PAGE_TOKENS - first_page;
   // with kept first tokens the last split is theirs: the pages before the window's first that
   // hold some of them (none when the window still reaches back to them)
-  const int run_splits = mask.keeps() ? n_splits - 1 : n_splits;
+  const int run_splits = opt.keeps() ? n_splits - 1 : n_splits;
   const int per_split = (n_pages + run_splits - 1) / run_splits;
-  const bool head_split = mask.keeps() && split == n_splits - 1;
+  const bool head_split = opt.keeps() && split == n_splits - 1;
   const int p_begin = head_split ? 0 : first_page + split * per_split;
   const int p_end = head_split ? min((keep_first + PAGE_TOKENS - 1) / PAGE_TOKENS, first_page)
                                : min(first_page + n_pages, p_begin + per_split);
@@ -228,6 +228,7 @@ attention_decode_kernel(const T* q, int q_stride, int q_col,
     const int head = kvh * group + gh;
     if (n_splits == 1) {   // nothing to merge with: this is the result
       if (sink != nullptr) a *= nb_sink_fix(l, M, sink[head], false);
+      a *= opt.gate_of(r, head);
       out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
       continue;
     }
@@ -264,6 +265,7 @@ attention_decode_kernel(const T* q, int q_stride, int q_col,
       l += f * __ldcg(&part_ml[(base + s) * 2 + 1]);
     }
     if (sink != nullptr) a *= nb_sink_fix(l, M, sink[head], false);
+    a *= opt.gate_of(r, head);
     out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
   }
 }
@@ -314,7 +316,7 @@ __global__ void __launch_bounds__(NW * 32)
 attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
                             const int* row_slot, const int* row_pos,
                             NbPagedKV kv, int group, TOut* out, int out_stride,
-                            float scale, float softcap, const float* sink, NbMask mask, int n_splits, float* part_acc,
+                            float scale, float softcap, const float* sink, NbAttnOpts opt, int n_splits, float* part_acc,
                             float* part_ml, int* counters, int append,
                             int k_col, int v_col) {
   typedef __nv_bfloat16 bf16;
@@ -364,15 +366,15 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
   }
   const int pos = row_pos[r];
   const int kv_len = pos + 1;
-  const int j_begin = mask.first_key(pos);
-  const int keep_first = mask.keeps() ? mask.keep_first : 0;
+  const int j_begin = opt.first_key(pos);
+  const int keep_first = opt.keeps() ? opt.keep_first : 0;
   const int first_page = j_begin / PAGE_TOKENS;
   const int n_pages = (kv_len + PAGE_TOKENS - 1) / PAGE_TOKENS - first_page;
   // with kept first tokens the last split is theirs: the pages before the window's first that
   // hold some of them (none when the window still reaches back to them)
-  const int run_splits = mask.keeps() ? n_splits - 1 : n_splits;
+  const int run_splits = opt.keeps() ? n_splits - 1 : n_splits;
   const int per_split = (n_pages + run_splits - 1) / run_splits;
-  const bool head_split = mask.keeps() && split == n_splits - 1;
+  const bool head_split = opt.keeps() && split == n_splits - 1;
   const int p_begin = head_split ? 0 : first_page + split * per_split;
   const int p_end = head_split ? min((keep_first + PAGE_TOKENS - 1) / PAGE_TOKENS, first_page)
                                : min(first_page + n_pages, p_begin + per_split);
@@ -601,6 +603,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
     const int head = kvh * group + gh;
     if (n_splits == 1) {
       if (sink != nullptr) a *= nb_sink_fix(l, M, sink[head], true);
+      a *= opt.gate_of(r, head);
       out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
       continue;
     }
@@ -641,6 +644,7 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
         l += f * row[s * step + HD + 1];
       }
       if (sink != nullptr) a *= nb_sink_fix(l, M, sink[kvh * group + gh], true);
+      a *= opt.gate_of(r, kvh * group + gh);
       out[(size_t)r * out_stride + (size_t)(kvh * group + gh) * HD + c] =
           nb_from_f32<TOut>(l > 0.0f ? a / l : a);
     }
@@ -688,13 +692,14 @@ attention_decode_mma_kernel(const __nv_bfloat16* q, int q_stride, int q_col,
       M = Mn;
     }
     if (sink != nullptr) a *= nb_sink_fix(l, M, sink[head], true);
+    a *= opt.gate_of(r, head);
     out[(size_t)r * out_stride + (size_t)head * HD + c] = nb_from_f32<TOut>(l > 0.0f ? a / l : a);
   }
 }
 
 template <int HD, typename TOut, int MMA_STAGES, int NW>
 int launch_mma_s(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
-                 const NbPagedKV& kv, int group, void* out, int out_stride, float scale, float softcap, const float* sink, NbMask mask,
+                 const NbPagedKV& kv, int group, void* out, int out_stride, float scale, float softcap, const float* sink, NbAttnOpts opt,
                  int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
                  int k_col, int v_col, bool clustered, cudaStream_t stream) {
   const size_t tiles = (size_t)2 * MMA_STAGES * PAGE_TOKENS * (HD + 8) * sizeof(__nv_bfloat16);
@@ -711,7 +716,7 @@ int launch_mma_s(const void* q, int q_stride, int q_col, const int* row_slot, co
     const size_t smem = tiles + (size_t)n_splits * group * (HD + 2) * sizeof(float);
     NB_CUDA(nb_launch_clusters(kern, grid, dim3(NW * 32), smem, stream, n_splits,
                                (const __nv_bfloat16*)q, q_stride, q_col, row_slot, row_pos, kv, group,
-                               (TOut*)out, out_stride, scale, softcap, sink, mask, n_splits, part_acc, part_ml,
+                               (TOut*)out, out_stride, scale, softcap, sink, opt, n_splits, part_acc, part_ml,
                                counters, append, k_col, v_col));
     return 0;
   }
@@ -722,14 +727,14 @@ int launch_mma_s(const void* q, int q_stride, int q_col, const int* row_slot, co
     configured = true;
   }
   NB_CUDA(nb_launch(kern, grid, dim3(NW * 32), tiles, stream, (const __nv_bfloat16*)q, q_stride, q_col,
-                    row_slot, row_pos, kv, group, (TOut*)out, out_stride, scale, softcap, sink, mask, n_splits,
+                    row_slot, row_pos, kv, group, (TOut*)out, out_stride, scale, softcap, sink, opt, n_splits,
                     part_acc, part_ml, counters, append, k_col, v_col));
   return 0;
 }
 
 template <int HD, typename TOut>
 int launch_mma(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
-               const NbPagedKV& kv, int group, void* out, int out_stride, float scale, float softcap, const float* sink, NbMask mask,
+               const NbPagedKV& kv, int group, void* out, int out_stride, float scale, float softcap, const float* sink, NbAttnOpts opt,
                int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
                int k_col, int v_col, bool clustered, cudaStream_t stream) {
   static int sms = 0;
@@ -749,20 +754,20 @@ int launch_mma(const void* q, int q_stride, int q_col, const int* row_slot, cons
   if (per_sm > 8) per_sm = 8;   // 2,048 threads an SM
   if (ctas <= per_sm * sms)
     return launch_mma_s<HD, TOut, 4, 8>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride,
-                                        scale, softcap, sink, mask, n_rows, n_splits, part_acc, part_ml, counters,
+                                        scale, softcap, sink, opt, n_rows, n_splits, part_acc, part_ml, counters,
                                         append, k_col, v_col, clustered, stream);
   return launch_mma_s<HD, TOut, 2, 4>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride,
-                                      scale, softcap, sink, mask, n_rows, n_splits, part_acc, part_ml, counters, append,
+                                      scale, softcap, sink, opt, n_rows, n_splits, part_acc, part_ml, counters, append,
                                       k_col, v_col, clustered, stream);
 }
 
 template <typename TOut>
 int mma_by_head_dim(int hd, const void* q, int q_stride, int q_col, const int* row_slot,
                     const int* row_pos, const NbPagedKV& kv, int group, void* out, int out_stride,
-                    float scale, float softcap, const float* sink, NbMask mask, int n_rows, int n_splits, float* pa, float* pm,
+                    float scale, float softcap, const float* sink, NbAttnOpts opt, int n_rows, int n_splits, float* pa, float* pm,
                     int* cn, int ap, int kc, int vc, bool clustered, cudaStream_t st) {
 #define NB_HD(HD_) \
-  case HD_: return launch_mma<HD_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, softcap, sink, mask, n_rows, n_splits, pa, pm, cn, ap, kc, vc, clustered, st)
+  case HD_: return launch_mma<HD_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, softcap, sink, opt, n_rows, n_splits, pa, pm, cn, ap, kc, vc, clustered, st)
   switch (hd) {
     NB_HD(16); NB_HD(32); NB_HD(48); NB_HD(64); NB_HD(80); NB_HD(96); NB_HD(112); NB_HD(128);
   }
@@ -772,7 +777,7 @@ int mma_by_head_dim(int hd, const void* q, int q_stride, int q_col, const int* r
 
 template <typename T, int HD, int G, typename TOut>
 int launch(const void* q, int q_stride, int q_col, const int* row_slot, const int* row_pos,
-           const NbPagedKV& kv, int group, void* out, int out_stride, float scale, float softcap, const float* sink, NbMask mask,
+           const NbPagedKV& kv, int group, void* out, int out_stride, float scale, float softcap, const float* sink, NbAttnOpts opt,
            int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters, int append,
            int k_col, int v_col, cudaStream_t stream) {
   const size_t smem = (size_t)4 * PAGE_TOKENS * HD * sizeof(T) +
@@ -782,7 +787,7 @@ int launch(const void* q, int q_stride, int q_col, const int* row_slot, const in
     NB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(n_splits, kv.n_kv_heads, n_rows);
   NB_CUDA(nb_launch(kern, grid, dim3(THREADS), smem, stream, (const T*)q, q_stride, q_col, row_slot,
-                    row_pos, kv, group, (TOut*)out, out_stride, scale, softcap, sink, mask, n_splits, part_acc,
+                    row_pos, kv, group, (TOut*)out, out_stride, scale, softcap, sink, opt, n_splits, part_acc,
                     part_ml, counters, append, k_col, v_col));
   return 0;
 }
@@ -790,10 +795,10 @@ int launch(const void* q, int q_stride, int q_col, const int* row_slot, const in
 template <typename T, int HD, typename TOut>
 int by_group(int group, const void* q, int q_stride, int q_col, const int* row_slot,
              const int* row_pos, const NbPagedKV& kv, void* out, int out_stride, float scale, float softcap,
-             const float* sink, NbMask mask, int n_rows, int n_splits, float* pa, float* pm, int* cn, int ap,
+             const float* sink, NbAttnOpts opt, int n_rows, int n_splits, float* pa, float* pm, int* cn, int ap,
              int kc, int vc, cudaStream_t st) {
 #define NB_G(G_) \
-  return launch<T, HD, G_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, softcap, sink, mask, n_rows, n_splits, pa, pm, cn, ap, kc, vc, st)
+  return launch<T, HD, G_, TOut>(q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, softcap, sink, opt, n_rows, n_splits, pa, pm, cn, ap, kc, vc, st)
   if (group == 1) NB_G(1);
   if (group == 2) NB_G(2);
   if (group <= 4) NB_G(4);
@@ -804,10 +809,10 @@ int by_group(int group, const void* q, int q_stride, int q_col, const int* row_s
 template <typename T, typename TOut>
 int by_head_dim(int hd, int group, const void* q, int q_stride, int q_col, const int* row_slot,
                 const int* row_pos, const NbPagedKV& kv, void* out, int out_stride, float scale, float softcap,
-                const float* sink, NbMask mask, int n_rows, int n_splits, float* pa, float* pm, int* cn, int ap,
+                const float* sink, NbAttnOpts opt, int n_rows, int n_splits, float* pa, float* pm, int* cn, int ap,
                 int kc, int vc, cudaStream_t st) {
 #define NB_HD(HD_) \
-  return by_group<T, HD_, TOut>(group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, softcap, sink, mask, n_rows, n_splits, pa, pm, cn, ap, kc, vc, st)
+  return by_group<T, HD_, TOut>(group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, softcap, sink, opt, n_rows, n_splits, pa, pm, cn, ap, kc, vc, st)
   switch (hd) {
     case 16: NB_HD(16);
     case 32: NB_HD(32);
@@ -848,7 +853,7 @@ std::atomic<int> g_cluster_merge{1};
 int attention_decode(const void* q, int dtype, int q_stride, int q_col, const int* row_slot,
                      const int* row_pos, const void* k_cache, const void* v_cache,
                      const int* block_table, int max_pages, int page, int n_heads, int n_kv_heads,
-                     int head_dim, void* out, int out_dtype, int out_stride, float scale, float softcap, const float* sink, NbMask mask,
+                     int head_dim, void* out, int out_dtype, int out_stride, float scale, float softcap, const float* sink, NbAttnOpts opt,
                      int n_rows, int n_splits, float* part_acc, float* part_ml, int* counters,
                      int append, int k_col, int v_col, int clusters_allowed, cudaStream_t stream) {
   if (n_rows == 0) return 0;
@@ -868,7 +873,7 @@ int attention_decode(const void* q, int dtype, int q_stride, int q_col, const in
   const int group = n_heads / n_kv_heads;
   typedef __nv_bfloat16 bf16;
   int rc;
-#define NB_ARGS head_dim, group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, softcap, sink, mask, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, stream
+#define NB_ARGS head_dim, group, q, q_stride, q_col, row_slot, row_pos, kv, out, out_stride, scale, softcap, sink, opt, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, stream
   if (dtype == NB_F32) {
     rc = out_dtype == NB_F32 ? by_head_dim<float, float>(NB_ARGS) : by_head_dim<float, bf16>(NB_ARGS);
   } else {
@@ -879,8 +884,8 @@ int attention_decode(const void* q, int dtype, int q_stride, int q_col, const in
     // through the scratch arrays and a counter
     const bool clustered = clusters_allowed > 0 && n_splits >= 2 && n_splits <= MAX_CLUSTER;
     rc = out_dtype == NB_F32
-             ? mma_by_head_dim<float>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, softcap, sink, mask, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, clustered, stream)
-             : mma_by_head_dim<bf16>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, softcap, sink, mask, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, clustered, stream);
+             ? mma_by_head_dim<float>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, softcap, sink, opt, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, clustered, stream)
+             : mma_by_head_dim<bf16>(head_dim, q, q_stride, q_col, row_slot, row_pos, kv, group, out, out_stride, scale, softcap, sink, opt, n_rows, n_splits, part_acc, part_ml, counters, append, k_col, v_col, clustered, stream);
   }
 #undef NB_ARGS
   if (rc) return rc;
@@ -899,14 +904,15 @@ NB_EXPORT int nb_attention_decode(const void* q, int dtype, int q_stride, int q_
                                   cudaStream_t stream) {
   return attention_decode(q, dtype, q_stride, q_col, row_slot, row_pos, k_cache, v_cache, block_table,
                           max_pages, page, n_heads, n_kv_heads, head_dim, out, out_dtype, out_stride,
-                          scale, 0.0f, nullptr, NbMask{window, 0, 0}, n_rows, n_splits, part_acc, part_ml,
+                          scale, 0.0f, nullptr, NbAttnOpts{window, 0, 0, nullptr, 0, 0}, n_rows, n_splits, part_acc, part_ml,
                           counters, append, k_col, v_col, g_cluster_merge.load(), stream);
 }
 
 // The same with capped scores (softcap > 0: a score becomes softcap * tanh(score / softcap)) and
 // a sink (fp32 [n_heads] logits of one more term of the softmax's denominator, without key or
-// value; null for none), and with the masks of NbMask (a window that keeps the sequence's first
-// tokens, which then take the last of the n_splits splits, or blocks of positions).  The step's keys and values are in the cache already, written by the
+// value; null for none), and with the options of NbAttnOpts (a window that keeps the sequence's first
+// tokens, which then take the last of the n_splits splits, or blocks of positions; a gate per
+// head).  The step's keys and values are in the cache already, written by the
 // kernel launched before this one: the pages are asked for only after that kernel is done.
 NB_EXPORT int nb_attention_decode_capped(const void* q, int dtype, int q_stride, int q_col,
                                          const int* row_slot, const int* row_pos,
@@ -915,18 +921,19 @@ NB_EXPORT int nb_attention_decode_capped(const void* q, int dtype, int q_stride,
                                          int n_heads, int n_kv_heads, int head_dim, void* out,
                                          int out_dtype, int out_stride, float scale, float softcap,
                                          const float* sink, int window, int keep_first,
-                                         int mask_block, int n_rows, int n_splits,
+                                         int mask_block, const float* gate, int gate_stride,
+                                         int gate_col, int n_rows, int n_splits,
                                          float* part_acc, float* part_ml, int* counters,
                                          cudaStream_t stream) {
   NB_REQUIRE(softcap >= 0.0f, NB_ERR_BAD_ARG, "attention_decode: a cap is positive, or 0 for none");
   NB_REQUIRE(window >= 0 && keep_first >= 0 && mask_block >= 0 && !(window > 0 && mask_block > 0),
              NB_ERR_BAD_ARG, "attention_decode: a mask is a window (with kept first tokens) or a block");
-  const NbMask mask{window, keep_first, mask_block};
-  NB_REQUIRE(!mask.keeps() || n_splits >= 2, NB_ERR_BAD_ARG,
+  const NbAttnOpts opt{window, keep_first, mask_block, gate, gate_stride, gate_col};
+  NB_REQUIRE(!opt.keeps() || n_splits >= 2, NB_ERR_BAD_ARG,
              "attention_decode: kept first tokens take a split of their own");
   return attention_decode(q, dtype, q_stride, q_col, row_slot, row_pos, k_cache, v_cache, block_table,
                           max_pages, page, n_heads, n_kv_heads, head_dim, out, out_dtype, out_stride,
-                          scale, softcap, sink, mask, n_rows, n_splits, part_acc, part_ml, counters,
+                          scale, softcap, sink, opt, n_rows, n_splits, part_acc, part_ml, counters,
                           /*append=*/-1, 0, 0, g_cluster_merge.load(), stream);
 }
 
@@ -1015,7 +1022,7 @@ NB_EXPORT int nb_attention_decode_static(const void* q, int dtype, int q_stride,
   // always through the scratch arrays: this entry point exists for them
   return attention_decode(q, dtype, q_stride, q_col, row_slot, row_pos, k_cache, v_cache,
                           block_table, max_pages, page, n_heads, n_kv_heads, head_dim, out,
-                          out_dtype, out_stride, scale, 0.0f, nullptr, NbMask{window, 0, 0}, n_rows,
+                          out_dtype, out_stride, scale, 0.0f, nullptr, NbAttnOpts{window, 0, 0, nullptr, 0, 0}, n_rows,
                           n_splits, reinterpret_cast<float*>(base + cnt_b + ml_b),
                           reinterpret_cast<float*>(base + cnt_b),
                           reinterpret_cast<int*>(base), /*append=*/0, 0, 0,

@@ -104,7 +104,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const int* seq_pos0, const int* block_table,
                             int max_pages, int n_kv_heads, int group, TOut* out,
                             int out_stride, float scale, float softcap,
-                            const float* __restrict__ sink, NbMask mask, int max_splits,
+                            const float* __restrict__ sink, NbAttnOpts opt, int max_splits,
                             int chunk_pages, float* part, int* counters,
                             int* err_word) {
   using L = AttnSmem<HD>;
@@ -150,9 +150,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int kvh = h / group;
   const int rows_here = min(TILE_Q, n_q - q0);
   const int last_pos = pos0 + q0 + rows_here - 1;                    // newest key any row sees
-  const int window = mask.window, block = mask.block;
-  const int keep_first = mask.keeps() ? mask.keep_first : 0;
-  const int first_key = mask.first_key(pos0 + q0);       // of the tile's first row: the earliest
+  const int window = opt.window, block = opt.block;
+  const int keep_first = opt.keeps() ? opt.keep_first : 0;
+  const int first_key = opt.first_key(pos0 + q0);       // of the tile's first row: the earliest
   // The pages this tile reads are cut into runs of chunk_pages, one CTA each (the long tiles of
   // a short batch would otherwise be a few long serial chains); the CTAs of a tile leave their
   // partial results in `part`, and the one that finishes last adds them up.  Kept first tokens
@@ -411,7 +411,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       unsigned long long vis = 0ull;
       if (has_keys) {
         const int hi = qpos - k0;                                   // keys 0..hi are not in the future
-        const int lo = mask.first_key(qpos) - k0;                   // keys lo.. are inside the window or block
+        const int lo = opt.first_key(qpos) - k0;                   // keys lo.. are inside the window or block
         const int kf = keep_first - k0;                             // keys ..kf-1 are kept first tokens
         const unsigned long long up = hi >= 63 ? ~0ull : (hi < 0 ? 0ull : ((2ull << hi) - 1ull));
         const unsigned long long dn = lo <= 0 ? ~0ull : (lo > 63 ? 0ull : (~0ull << lo));
@@ -562,7 +562,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         fix = (m_run == -INFINITY) ? 0.0f : nb_exp2(m_run - m_f);
         l_run = fmaf(l_run, fix, nb_exp2(sk - m_f));
       }
-      const float inv = l_run > 0.0f ? fix / l_run : 0.0f;
+      const float inv = (l_run > 0.0f ? fix / l_run : 0.0f) * opt.gate_of(row0 + q0 + r, h);
       TOut* dst = out + (size_t)(row0 + q0 + r) * out_stride + (size_t)h * HD + half * OC;
       if constexpr (sizeof(TOut) == 2) {
 #pragma unroll
@@ -614,7 +614,7 @@ template <int HD, typename TOut, bool CAP>
 int launch_tc(const void* q, int q_stride, int q_col, int n_rows, const int* cu_rows,
               const int* seq_slot, const int* seq_pos0, const void* k_cache, const void* v_cache,
               long long n_pages, const int* block_table, int max_pages, int n_heads, int n_kv_heads,
-              void* out, int out_stride, float scale, float softcap, const float* sink, NbMask mask,
+              void* out, int out_stride, float scale, float softcap, const float* sink, NbAttnOpts opt,
               int n_seqs, int max_q_len, int max_splits, int chunk_pages, float* part,
               int* counters, int append, int k_col, int v_col, cudaStream_t stream) {
   using L = AttnSmem<HD>;
@@ -637,7 +637,7 @@ int launch_tc(const void* q, int q_stride, int q_col, int n_rows, const int* cu_
   dim3 grid(((max_q_len + TILE_Q - 1) / TILE_Q) * max_splits, n_heads, n_seqs);
   NB_CUDA(nb_launch(kern, grid, dim3(TC_THREADS), (size_t)L::TOTAL, stream, mq, mk, mv, mn, append, k_col,
                     v_col, q_col, cu_rows, seq_slot, seq_pos0, block_table, max_pages, n_kv_heads,
-                    n_heads / n_kv_heads, (TOut*)out, out_stride, scale, softcap, sink, mask,
+                    n_heads / n_kv_heads, (TOut*)out, out_stride, scale, softcap, sink, opt,
                     max_splits, chunk_pages, part, counters, error_word()));
   return 0;
 }
@@ -686,7 +686,7 @@ NB_EXPORT int nb_attention_prefill_tc_record(int head_dim) { return 2 * TILE_Q +
 // head after head); every seq_pos0 must then be a multiple of the page size, and the kernel
 // writes them to the cache itself.  softcap > 0: a score becomes softcap * tanh(score /
 // softcap); sink: fp32 [n_heads] logits of one more term of the softmax's denominator, or null.
-// window / keep_first / mask_block: the masks of NbMask.  With kept first tokens (window > 0 and
+// window / keep_first / mask_block, gate: the options of NbAttnOpts.  With kept first tokens (window > 0 and
 // keep_first > 0) the last of the max_splits runs is theirs: max_splits >= 2, and the runs before
 // it, max_splits - 1 of chunk_pages pages, must cover what a tile's window spans.
 NB_EXPORT int nb_attention_prefill_tc_masked(const void* q, int dtype, int q_stride, int q_col, int n_rows,
@@ -696,14 +696,15 @@ NB_EXPORT int nb_attention_prefill_tc_masked(const void* q, int dtype, int q_str
                                       int n_kv_heads, int head_dim, void* out, int out_dtype,
                                       int out_stride, float scale, float softcap,
                                       const float* sink, int window, int keep_first, int mask_block,
+                                      const float* gate, int gate_stride, int gate_col,
                                       int n_seqs, int max_q_len, int max_splits, int chunk_pages,
                                       float* part, int* counters, int append, int k_col, int v_col,
                                       cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return 0;
   NB_REQUIRE(window >= 0 && keep_first >= 0 && mask_block >= 0 && !(window > 0 && mask_block > 0),
              NB_ERR_BAD_ARG, "attention_prefill_tc: a mask is a window (with kept first tokens) or a block");
-  const NbMask mask{window, keep_first, mask_block};
-  NB_REQUIRE(!mask.keeps() || max_splits >= 2, NB_ERR_BAD_ARG,
+  const NbAttnOpts opt{window, keep_first, mask_block, gate, gate_stride, gate_col};
+  NB_REQUIRE(!opt.keeps() || max_splits >= 2, NB_ERR_BAD_ARG,
              "attention_prefill_tc: kept first tokens take a run of their own");
   NB_REQUIRE(nb_attention_prefill_tc_supported(dtype, head_dim, n_heads, n_kv_heads, page, q_stride,
                                                q_col, out_dtype, out_stride),
@@ -727,7 +728,7 @@ NB_EXPORT int nb_attention_prefill_tc_masked(const void* q, int dtype, int q_str
                  (uintptr_t)out % 16 == 0,
              NB_ERR_UNSUPPORTED, "attention_prefill_tc: operands must be 16-byte aligned");
   int rc = NB_ERR_UNSUPPORTED;
-#define NB_ARGS q, q_stride, q_col, n_rows, cu_rows, seq_slot, seq_pos0, k_cache, v_cache, (long long)n_pages, block_table, max_pages, n_heads, n_kv_heads, out, out_stride, scale, softcap, sink, mask, n_seqs, max_q_len, max_splits, chunk_pages, part, counters, append, k_col, v_col, stream
+#define NB_ARGS q, q_stride, q_col, n_rows, cu_rows, seq_slot, seq_pos0, k_cache, v_cache, (long long)n_pages, block_table, max_pages, n_heads, n_kv_heads, out, out_stride, scale, softcap, sink, opt, n_seqs, max_q_len, max_splits, chunk_pages, part, counters, append, k_col, v_col, stream
   NB_REQUIRE(softcap >= 0.0f, NB_ERR_BAD_ARG, "attention_prefill_tc: a cap is positive, or 0 for none");
   if (softcap > 0.0f) {
     if (head_dim == 64)
@@ -758,9 +759,9 @@ NB_EXPORT int nb_attention_prefill_tc_capped(const void* q, int dtype, int q_str
   return nb_attention_prefill_tc_masked(q, dtype, q_stride, q_col, n_rows, cu_rows, seq_slot, seq_pos0,
                                         k_cache, v_cache, n_pages, block_table, max_pages, page,
                                         n_heads, n_kv_heads, head_dim, out, out_dtype, out_stride,
-                                        scale, softcap, sink, window, 0, 0, n_seqs, max_q_len,
-                                        max_splits, chunk_pages, part, counters, append, k_col, v_col,
-                                        stream);
+                                        scale, softcap, sink, window, 0, 0, nullptr, 0, 0, n_seqs,
+                                        max_q_len, max_splits, chunk_pages, part, counters, append,
+                                        k_col, v_col, stream);
 }
 
 // The same without cap and sink.

@@ -515,7 +515,7 @@ class CudaBackend:
                            _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), kv.block_table.shape[1],
                            kv.page, n_heads, kv.n_kv_heads, kv.head_dim, _ptr(out),
                            dtype_code(out.dtype), out.shape[1], scale, float(softcap or 0.0),
-                           _ptr(sink), window, 0, 0, n_rows, n_splits, _ptr(acc), _ptr(ml),
+                           _ptr(sink), window, 0, 0, _ptr(None), 0, 0, n_rows, n_splits, _ptr(acc), _ptr(ml),
                            _ptr(counters), self._stream())
                 return
             self._call("nb_attention_decode", _ptr(q_src), dtype_code(q_src.dtype),
@@ -769,7 +769,8 @@ class CudaBackend:
         if shared and q.dtype == k_store.k.dtype and layout.is_decode and \
                 self.lib.nb_attention_decode_supported(code, d, n_heads, k_store.n_kv_heads, k_store.page) \
                 and (q.dtype != torch.bfloat16 or q.shape[1] % 8 == 0):
-            # one-token steps: the split decode kernel; kept first tokens are its last split
+            # one-token steps: the split decode kernel; kept first tokens are its last split, the
+            # gate is applied where a row's sum divides its result
             pages = max(1, -(-layout.max_kv_len // k_store.page))
             if look_back > 0:
                 pages = min(pages, (look_back + k_store.page - 1) // k_store.page + 1)
@@ -780,9 +781,8 @@ class CudaBackend:
                        _ptr(k_store.block_table), k_store.block_table.shape[1], k_store.page, n_heads,
                        k_store.n_kv_heads, d, _ptr(out), dtype_code(out.dtype), out.shape[1],
                        float(scale), float(softcap or 0.0), _ptr(sink), int(window), int(keep_first),
-                       int(chunk), n, n_splits, _ptr(acc), _ptr(ml), _ptr(counters), self._stream())
-            if gate is not None:
-                self.head_gate(out, gate, gate_col, n_heads, dv)
+                       int(chunk), _ptr(gate), gate.shape[1] if gate is not None else 0, int(gate_col),
+                       n, n_splits, _ptr(acc), _ptr(ml), _ptr(counters), self._stream())
             return
         if shared and q.dtype == k_store.k.dtype and not layout.is_decode and self.use_tcgen05 \
                 and scale > 0 and self.lib.nb_attention_prefill_tc_supported(
@@ -812,10 +812,9 @@ class CudaBackend:
                        k_store.block_table.shape[1], k_store.page, n_heads, k_store.n_kv_heads, d,
                        _ptr(out), dtype_code(out.dtype), out.shape[1], float(scale),
                        float(softcap or 0.0), _ptr(sink), int(window), int(keep_first), int(chunk),
+                       _ptr(gate), gate.shape[1] if gate is not None else 0, int(gate_col),
                        layout.n_seqs, layout.max_q_len, max_splits, per_run, _ptr(part),
                        _ptr(counters), 0, 0, 0, self._stream())
-            if gate is not None:
-                self.head_gate(out, gate, gate_col, n_heads, dv)
             return
         # any sizes and types, fp32 arithmetic: the 32-bit path, and what the kernels above leave
         v_plane = k_store.v if shared else v_store.k
@@ -827,15 +826,6 @@ class CudaBackend:
                    float(scale), float(softcap or 0.0), int(window), int(keep_first), int(chunk),
                    _ptr(gate), gate.shape[1] if gate is not None else 0, int(gate_col), n,
                    self._stream())
-
-    def head_gate(self, x, gate, gate_col, n_heads, dv):
-        """``x[r, h * dv + c] *= sigmoid(gate[r, gate_col + h])`` in place (``gate``: fp32 rows)."""
-        _check(x, "x", None, 2)
-        _check(gate, "gate", torch.float32, 2)
-        if x.shape[1] != n_heads * dv or gate.shape[0] < x.shape[0] or gate.shape[1] < gate_col + n_heads:
-            raise KernelError("head_gate: shapes do not agree")
-        self._call("nb_head_gate", _ptr(x), dtype_code(x.dtype), _ptr(gate), gate.shape[1],
-                   int(gate_col), n_heads, dv, x.shape[0], self._stream())
 
     def pool_blocks(self, layout, kv, blocks, pool):
         """For every row that completes a block of ``pool`` tokens: the means of the block's keys

@@ -798,43 +798,6 @@ NB_EXPORT int nb_glu_rows(const float* x, int x_stride, int gate_col, int up_col
 }
 
 // ---------------------------------------------------------------------------------
-// x[r, h * dv + c] *= sigmoid(gate[r, gate_col + h]): a gate per head on the heads' results, in
-// place (for attention kernels that do not apply it themselves).
-// ---------------------------------------------------------------------------------
-template <typename T>
-__global__ void head_gate_kernel(T* x, const float* gate, int gate_stride, int gate_col, int n_heads,
-                                 int dv, size_t total) {
-  nb_grid_dependency_wait();
-  nb_launch_dependents();
-  const int width = n_heads * dv;
-  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
-       e += (size_t)gridDim.x * blockDim.x) {
-    const size_t r = e / width;
-    const int h = (int)(e - r * width) / dv;
-    x[e] = nb_from_f32<T>(nb_to_f32(x[e]) * nb_sigmoid(gate[r * gate_stride + gate_col + h]));
-  }
-}
-
-NB_EXPORT int nb_head_gate(void* x, int dtype, const float* gate, int gate_stride, int gate_col,
-                           int n_heads, int dv, int n_rows, cudaStream_t stream) {
-  if (n_rows == 0) return 0;
-  NB_REQUIRE(n_rows > 0 && n_heads > 0 && dv > 0 && gate_col >= 0 && gate_stride >= gate_col + n_heads,
-             NB_ERR_BAD_ARG, "head_gate: bad sizes rows=%d heads=%d dv=%d", n_rows, n_heads, dv);
-  const size_t total = (size_t)n_rows * n_heads * dv;
-  const int blocks = (int)((total + 1023) / 1024 < 148 * 8 ? (total + 1023) / 1024 : 148 * 8);
-  if (dtype == NB_F32)
-    NB_CUDA(nb_launch(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, gate,
-                      gate_stride, gate_col, n_heads, dv, total));
-  else if (dtype == NB_BF16)
-    NB_CUDA(nb_launch(head_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
-                      (__nv_bfloat16*)x, gate, gate_stride, gate_col, n_heads, dv, total));
-  else
-    NB_REQUIRE(false, NB_ERR_BAD_ARG, "head_gate: unknown dtype %d", dtype);
-  NB_CHECK_LAUNCH("head_gate");
-  return 0;
-}
-
-// ---------------------------------------------------------------------------------
 // out[r, out_col + i] = x[r, i] for fp32 rows x, into rows of stride out_stride of another type:
 // the stream as the operand of a product, written beside other columns of the same operand.
 // ---------------------------------------------------------------------------------

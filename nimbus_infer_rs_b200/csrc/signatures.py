@@ -12,7 +12,7 @@ SIGNATURES = {
     "nb_attention_decode_scratch": "iiiiippp",
     "nb_attention_decode": "piiipppppiiiiipiifiiipppiiip",
     "nb_attention_decode_static": "piiipppppiiiiipiifiiip",
-    "nb_attention_decode_capped": "piiipppppiiiiipiiffpiiiiipppp",
+    "nb_attention_decode_capped": "piiipppppiiiiipiiffpiiipiiiipppp",
     "nb_attention_decode_cluster_merge": "i",
     "nb_attention_decode_cluster_limit": "",
     "nb_attention_generic": "piiipppppiiiiipiifiip",
@@ -25,7 +25,7 @@ SIGNATURES = {
     "nb_attention_prefill_tc_set_wait_budget": "l",
     "nb_attention_prefill_tc": "piiiipppppipiiiiipiifiiiiippiiip",
     "nb_attention_prefill_tc_capped": "piiiipppppipiiiiipiiffpiiiiippiiip",
-    "nb_attention_prefill_tc_masked": "piiiipppppipiiiiipiiffpiiiiiiippiiip",
+    "nb_attention_prefill_tc_masked": "piiiipppppipiiiiipiiffpiiipiiiiiippiiip",
     "nb_attention_prefill_tc_record": "i",
     "nb_gemm_simt": "pipipppiiiiip",
     "nb_gemm_skinny": "pippfpipppiiiiip",
@@ -73,7 +73,6 @@ SIGNATURES = {
     "nb_selective_scan": "ppiiipppppiipippiipiip",
     "nb_linear_attention_supported": "ii",
     "nb_linear_attention": "piiiiippippiiipip",
-    "nb_head_gate": "pipiiiiip",
     "nb_glu_rows": "piiiifpiiip",
     "nb_cast_cols": "ppiiiiip",
     "nb_rmsnorm_gated": "pppiipiiifp",
