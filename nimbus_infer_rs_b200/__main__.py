@@ -8,7 +8,7 @@
 
 Instead of ``--model DIR`` every command but ``random`` takes ``--random PRESET --seed-weights
 S``: a model of a named size (``gpt2`` = the reference's defaults, src/config.rs:45-66;
-``gpt2-medium``, ``gpt2-xl``, ``tiny-a``, ``tiny-b``, ``runesun-tiny``, ``rizitar-tiny`` ...) with seeded random weights, no file on disk.
+``gpt2-medium``, ``gpt2-xl``, ``tiny-a``, ``tiny-b``, ``runesun-tiny``, ``rizitar-tiny``, ``pinozen-tiny``, ``lulizen-tiny`` ...) with seeded random weights, no file on disk.
 
 Flag names, meanings and defaults follow the reference where it has them (``--model``,
 ``--ids``, ``--max-new-tokens`` 64, ``--temperature`` 0 = greedy, ``--top-k`` 0, ``--top-p``
@@ -46,7 +46,7 @@ def _common(ap):
     ap.add_argument("--model", help="folder with config.json and the weight file")
     ap.add_argument("--random", metavar="PRESET",
                     help="instead of --model: a model of a named size with seeded random weights "
-                         "(gpt2, gpt2-medium, gpt2-xl, tiny-a, tiny-b, runesun-tiny, rizitar-tiny, ...); nothing is read from disk")
+                         "(gpt2, gpt2-medium, gpt2-xl, tiny-a, tiny-b, runesun-tiny, rizitar-tiny, pinozen-tiny, lulizen-tiny, ...); nothing is read from disk")
     ap.add_argument("--seed-weights", type=int, default=0, help="seed of --random's weights")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--device", default="cuda:0")
@@ -250,7 +250,7 @@ def main(argv=None) -> int:
     r = sub.add_parser("random")
     r.add_argument("--out", required=True)
     r.add_argument("--config", help="a config.json to take the sizes from")
-    r.add_argument("--preset", help="or a named size: gpt2, gpt2-medium, gpt2-xl, tiny-a, tiny-b, runesun-tiny, rizitar-tiny, ... (config/presets/)")
+    r.add_argument("--preset", help="or a named size: gpt2, gpt2-medium, gpt2-xl, tiny-a, tiny-b, runesun-tiny, rizitar-tiny, pinozen-tiny, lulizen-tiny, ... (config/presets/)")
     r.add_argument("--seed", type=int, default=0)
     r.add_argument("--std", type=float, default=None, help="spread of the matrices (0.02)")
     r.add_argument("--bias-std", type=float, default=None,

@@ -3,6 +3,8 @@ previous token in a state row, paged stores that keep a sequence's first pages, 
 with another layer's tensors and storage of their own, slots, pages, batches, the generation
 loop) on the torch-CPU stand-in of the kernel library, against the plain implementation."""
 import copy
+import io
+import json
 import math
 
 import pytest
@@ -274,3 +276,34 @@ def test_random_weights_mode_and_inspect(cpu_backend):
     assert e.model.n_params() >= cfg.n_params()       # fused products are filled up with zeros
     small = Engine.random("lulizen-tiny", seed=1, dtype="float32", device="cpu", cache_tokens=256)
     assert small.step([(small.alloc_slot(), [5, 6], [1])]).shape[0] == 1
+
+
+def test_command_line_and_trace_replay_take_the_design(cpu_backend, tmp_path, monkeypatch, capsys):
+    """`random` writes a Lulizen folder that loads again; trace replay drives it with the cache
+    the token budget gives, across a portion's start (the token before it is in the state row)."""
+    import importlib.machinery
+    import importlib.util
+    from pathlib import Path
+
+    import numpy as np
+    from nimbus_infer_rs_b200.__main__ import main as cli
+    folder = tmp_path / "m"
+    assert cli(["random", "--preset", "lulizen-tiny", "--out", str(folder), "--seed", "5"]) == 0
+    assert json.loads((folder / "config.json").read_text())["architecture"] == "Lulizen"
+    capsys.readouterr()
+    e = Engine.load(folder, dtype="float32", device="cpu", cache_tokens=128)
+    want = e.step([(e.alloc_slot(), [3, 1, 4, 1, 5], [0, 4])])
+    path = Path(__file__).resolve().parent.parent / "bin" / "trace_run"
+    spec = importlib.util.spec_from_loader("trace_run_cli", importlib.machinery.SourceFileLoader(
+        "trace_run_cli", str(path)))
+    tr = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(tr)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": [3, 1, 4], "want": [0]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": [1, 5], "want": [1]}], "end": ["a"]}]
+    monkeypatch.setattr("sys.stdin", io.StringIO("".join(json.dumps(s) + "\n" for s in steps)))
+    monkeypatch.setattr("sys.argv", ["trace_run", "--model", str(folder), "--dtype", "float32",
+                                     "--out", str(tmp_path / "o"), "--max-tokens", "5", "--device", "cpu"])
+    assert tr.main() == 0
+    assert capsys.readouterr().out.split() == ["done", "0", "done", "1"]
+    got = np.concatenate([np.fromfile(tmp_path / "o" / f"{i}.f32", dtype="<f4") for i in (0, 1)])
+    _close(torch.from_numpy(got).view(2, -1), want)
