@@ -123,29 +123,41 @@ def weight_plan(cfg: LulizenConfig, spec: ModelSpec, names: set[str]) -> WeightP
             r[L + "ffn.proj.weight"] = take(p + "mlp.down", (D, ff.ff))
         else:
             E, F = ff.experts, ff.expert.ff
-            r[L + "ffn.router.weight"] = take(p + "mlp.router", (E, D))
+            if ff.shared is None:
+                r[L + "ffn.router.weight"] = take(p + "mlp.router", (E, D))
             if ff.correction:
                 r[L + "ffn.correction"] = take(p + "mlp.correction", (E,))
             r[L + "ffn.gate"] = _stack([f"{p}mlp.e{k}.gate" for k in range(E)], (F, D))
             r[L + "ffn.up"] = _stack([f"{p}mlp.e{k}.up" for k in range(E)], (F, D))
             r[L + "ffn.down"] = _stack([f"{p}mlp.e{k}.down" for k in range(E)], (D, F))
             if ff.shared is not None:
-                r[L + "ffn.shared.fc.weight"] = _gate_up(p + "mlp.shared.", ff.shared.ff, D)
+                # the router's rows ride under the shared expert's gate and up halves
+                r[L + "ffn.shared.fc.weight"] = _gate_up(p + "mlp.shared.", ff.shared.ff, D,
+                                                         extra=(p + "mlp.router", E))
                 r[L + "ffn.shared.proj.weight"] = take(p + "mlp.shared.down", (D, ff.shared.ff))
     return WeightPlan(r, ignored)
 
 
-def _gate_up(prefix: str, hidden: int, width: int) -> Recipe:
+def _gate_up(prefix: str, hidden: int, width: int, extra: tuple[str, int] | None = None) -> Recipe:
     """Gate and up one under the other, each half filled with rows of zeros up to a multiple of
-    8 rows (the layout of ``gated_mlp``'s first product)."""
-    half = -(-hidden // 8) * 8
-    if half == hidden:
-        return _rows([(prefix + "gate", (hidden, width)), (prefix + "up", (hidden, width))])
-    inner = _rows([(prefix + "gate", (hidden, width)), (prefix + "up", (hidden, width))])
+    8 rows (the layout of ``gated_mlp``'s first product); ``extra`` = (name, rows): one more
+    matrix under them, filled up likewise."""
+    named = [(prefix + "gate", (hidden, width)), (prefix + "up", (hidden, width))]
+    if extra is not None:
+        named.append((extra[0], (extra[1], width)))
+    inner = _rows(named)
 
     def combine(ts):
-        pad = torch.zeros((half - hidden, width), dtype=ts[0].dtype)
-        return torch.cat([ts[0], pad, ts[1].to(ts[0].dtype), pad], dim=0).contiguous()
+        kinds = {t.dtype for t in ts}
+        if len(kinds) > 1:
+            ts = [t.to(torch.float32) for t in ts]
+        out = []
+        for t in ts:
+            out.append(t)
+            pad = -t.shape[0] % 8
+            if pad:
+                out.append(torch.zeros((pad, width), dtype=t.dtype))
+        return torch.cat(out, dim=0).contiguous()
     return Recipe(inner.sources, combine)
 
 

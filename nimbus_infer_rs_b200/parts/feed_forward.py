@@ -62,11 +62,16 @@ class GatedMLP(FeedForward):
 
     One product gives ``[Wgate h | Wup h]`` side by side in fp32; a row pass applies the
     activation to the first half, multiplies by the second (both unrounded) and hands the
-    product to ``Wdown`` in the activation type."""
+    product to ``Wdown`` in the activation type.
+
+    ``extra_outputs`` > 0: that many more rows of weights ride on the first product for another
+    reader of the same rows (a router beside a shared expert); their fp32 results are left in
+    ``ctx.shared_projection`` as ``(rows, first column)``."""
     graph_safe = True
     can_overwrite = True
 
-    def __init__(self, width: int, hidden: int, activation: str, limit: float | None = None):
+    def __init__(self, width: int, hidden: int, activation: str, limit: float | None = None,
+                 extra_outputs: int = 0):
         if activation not in GLU_ACTIVATIONS:
             raise ValueError(f"unknown activation {activation!r} (have {sorted(GLU_ACTIVATIONS)})")
         if (limit is not None) != (activation in PARAM_ACTIVATIONS):
@@ -77,7 +82,8 @@ class GatedMLP(FeedForward):
         self.act_code = GLU_ACTIVATIONS[activation]
         # the two halves start on multiples of 8 columns (fp32 rows on 32-byte boundaries)
         self.half = -(-self.hidden // 8) * 8
-        self.fc = Linear(self.width, 2 * self.half, bias=False)
+        self.extra_outputs = int(extra_outputs)
+        self.fc = Linear(self.width, 2 * self.half + -(-self.extra_outputs // 8) * 8, bias=False)
         self.proj = Linear(self.hidden, self.width, bias=False)
 
     def children(self):
@@ -85,6 +91,8 @@ class GatedMLP(FeedForward):
 
     def forward(self, ctx, h: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
         both = self.fc(ctx, h, out_dtype=torch.float32)
+        if self.extra_outputs:
+            ctx.shared_projection = (both, 2 * self.half)
         mid = torch.empty((both.shape[0], self.hidden), device=both.device, dtype=ctx.rt.act_dtype)
         ctx.ops.glu_rows(both, 0, self.half, self.act_code, mid, self.act_param)
         if accumulate:

@@ -28,7 +28,8 @@ class RoutedExperts(FeedForward):
     divided by ``sum + norm_eps``, times ``route_scale``.  Gated experts may combine their halves
     by ``swish_clamp`` with the bound ``limit`` (``parts/feed_forward.py``).  With ``shared`` (a
     mapping with ``hidden``, ``activation``, ``limit``) one more gated feed-forward of that size
-    runs for every token and is added.
+    runs for every token and is added; the router's weight rows then ride on that expert's first
+    product (the rows under its gate and up halves), and this part has no router product.
 
     The router's logits are a product of the same rows as the mixer's projections in a block
     whose sublayers share one norm; ``router_from_mixer`` then reads them from the columns the
@@ -62,9 +63,11 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"{groups} groups (keep {keep_groups}) do not fit {n_experts} experts, top={top}")
         self.route_scale, self.norm_eps = float(route_scale), float(norm_eps)
         self.act_param = float(limit) if limit is not None else 0.0
-        self.shared = None if not shared else GatedMLP(int(width), int(shared["hidden"]),
-                                                       shared.get("activation", activation),
-                                                       shared.get("limit"))
+        # the shared expert's first product also gives the router's logits (one read of the rows)
+        self.router_from_shared = bool(shared) and not router_from_mixer
+        self.shared = None if not shared else GatedMLP(
+            int(width), int(shared["hidden"]), shared.get("activation", activation),
+            shared.get("limit"), extra_outputs=int(n_experts) if self.router_from_shared else 0)
         self.width, self.n_experts, self.top, self.hidden = int(width), int(n_experts), int(top), int(hidden)
         if not 1 <= self.top <= self.n_experts:
             raise ValueError(f"top={top} of {n_experts} experts")
@@ -73,7 +76,8 @@ class RoutedExperts(FeedForward):
         self.renormalize = bool(renormalize)
         self.router_from_mixer = bool(router_from_mixer)
         self.gated = bool(gated)
-        self.router = None if self.router_from_mixer else Linear(self.width, self.n_experts, bias=False)
+        self.router = None if (self.router_from_mixer or self.router_from_shared) \
+            else Linear(self.width, self.n_experts, bias=False)
         self.gate = self.up = self.down = self.correction = None
 
     def children(self):
@@ -101,7 +105,7 @@ class RoutedExperts(FeedForward):
             residual.zero_()
         lay, ops, dev = ctx.layout, ctx.ops, h.device
         n, top = lay.n_rows, self.top
-        if self.router_from_mixer:
+        if self.router_from_mixer or self.router_from_shared:
             logits, col = ctx.shared_projection
         else:
             logits, col = self.router(ctx, h, out_dtype=torch.float32), 0
