@@ -24,3 +24,8 @@ class StepContext:
     shared_projection: Any = None
     # buffers that a part keeps for the rest of the step (keyed by the part)
     scratch: dict = field(default_factory=dict)
+    # the first norm of the schedule entry that runs next, if that entry's arrangement takes its
+    # normed rows from the arrangement before it (which then computes them in its last pass over
+    # the stream and leaves them in ``normed``)
+    next_norm: Any = None
+    normed: Any = None

@@ -142,9 +142,18 @@ class Model:
             layer = self.layers[li]
             if entry in self.stream_input_before:
                 x = self.stream_input.forward(ctx, x, x0)
+                ctx.normed = None
             ctx.kv, ctx.state, ctx.writes_cache = self.storage_of(ctx.cache, entry)
             ctx.kv_extra = ctx.cache.layer_kv_extra(entry)
+            # an arrangement whose last pass over the stream can also norm it for the entry that
+            # runs next is told that entry's first norm
+            ctx.next_norm = None
+            if entry + 1 < len(self.run_order) and entry + 1 not in self.stream_input_before:
+                nxt = self.layers[self.run_order[entry + 1]]
+                if getattr(nxt.block, "takes_handed_norm", False):
+                    ctx.next_norm = nxt.norm_mixer
             layer.block.forward(ctx, x, layer)
+        ctx.next_norm = ctx.normed = None
         return x
 
     def storage_requests(self):

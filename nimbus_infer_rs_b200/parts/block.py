@@ -60,8 +60,11 @@ class SandwichBlock(Block):
     A sublayer writes its result into an fp32 buffer of its own (a part that cannot overwrite
     gets zeros to add to); one pass over the rows norms that result, adds it to the stream and
     produces what the next reader wants: the next sublayer's normed rows, or the stream rounded
-    to the activation type for the per-token input."""
+    to the activation type for the per-token input, or (``ctx.next_norm``) the normed rows the
+    next layer's mixer reads, which that layer then finds in ``ctx.normed`` and does not compute
+    again."""
     graph_safe = True
+    takes_handed_norm = True
 
     def __init__(self):
         pass
@@ -80,13 +83,17 @@ class SandwichBlock(Block):
         side = layer.side
         # the side input multiplies the stream by a matrix: in a 32-bit run the stream itself
         wants_rounded = side is not None and ctx.rt.act_dtype != torch.float32
-        h = layer.norm_mixer.forward(ctx, x)
+        h, ctx.normed = ctx.normed, None
+        if h is None:
+            h = layer.norm_mixer.forward(ctx, x)
         y = self._run(layer.mixer, ctx, h, x)
+        last = layer.post_norm_ffn if layer.ffn is not None else layer.post_norm_mixer
+        # the next layer's first norm in the last pass: only if nothing changes the stream after
+        # that pass, and the two norms are of one kind (one kernel norms both ways)
+        then = ctx.next_norm if side is None and type(ctx.next_norm) is type(last) else None
         if layer.ffn is not None:
             h, _ = layer.post_norm_mixer.add_into(ctx, y, x, then=layer.norm_ffn)
             y = self._run(layer.ffn, ctx, h, x)
-            _, xr = layer.post_norm_ffn.add_into(ctx, y, x, rounded=wants_rounded)
-        else:
-            _, xr = layer.post_norm_mixer.add_into(ctx, y, x, rounded=wants_rounded)
+        ctx.normed, xr = last.add_into(ctx, y, x, then=then, rounded=wants_rounded)
         if side is not None:
             side.forward(ctx, x, xr if wants_rounded else x)
