@@ -52,14 +52,19 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // EXTRA: the kernel also takes a second paged store of pooled blocks (entry b = the mean key
 // and mean value of tokens b*pool .. b*pool+pool-1; row i sees it once b*pool + pool - 1 <=
 // i - window) whose pages are walked before the window's, and a sink per head: one more term
-// exp(sink_h) of the softmax's denominator, without a key, a value or the score scale.
+// exp(sink_h) of the softmax's denominator, without a key, a value or the score scale.  Or, in
+// place of the blocks, the options of NbAttnOpts: a window that keeps the sequence's first tokens
+// (their pages, where they lie before the window's, are the units walked first), a mask by blocks
+// of positions, a gate per head; and with softcap > 0 scores bent by softcap * tanh(score /
+// softcap).
 template <int HD, typename TOut, bool EXTRA>
 __global__ void __launch_bounds__(THREADS)
 attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
                          const int* __restrict__ cu_rows, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_pos0, NbPagedKV kv, int group,
                          TOut* __restrict__ out, int out_stride, float scale, int window,
-                         NbPagedKV blocks, int pool, const float* __restrict__ sink) {
+                         NbPagedKV blocks, int pool, const float* __restrict__ sink,
+                         NbAttnOpts opt, float softcap) {
   constexpr int ROW = HD + 8;              // padded row (elements): ldmatrix without conflicts
   constexpr int KS = HD / 16;              // k-steps of the score product
   constexpr int NT = HD / 8;               // n-tiles of the value product
@@ -85,19 +90,24 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
   const int g = lane >> 2, t = lane & 3;
   const int rows_here = min(BLOCK_Q, n_q - q0);
   const int last_pos = pos0 + q0 + rows_here - 1;                    // newest key any row sees
-  const int first_key = (window > 0) ? max(0, pos0 + q0 + 1 - window) : 0;
+  const int first_key = EXTRA ? opt.first_key(pos0 + q0)
+                              : ((window > 0) ? max(0, pos0 + q0 + 1 - window) : 0);
   const int p_begin = first_key / PAGE_TOKENS, p_end = last_pos / PAGE_TOKENS + 1;
   const int* table = kv.block_table + (size_t)slot * kv.max_pages;
   // blocks the tile's last row sees, and their pages: walked first, as units 0 .. n_bpages - 1
   const int nb_tile = (EXTRA && pool > 0 && window > 0 && blocks.k != nullptr)
                           ? max(0, (last_pos + 1 - window) / pool) : 0;
-  const int n_bpages = (nb_tile + PAGE_TOKENS - 1) / PAGE_TOKENS;
-  const int* btable = (EXTRA && n_bpages > 0) ? blocks.block_table + (size_t)slot * blocks.max_pages : nullptr;
+  // or the pages of kept first tokens that lie before the window's first page
+  const int keep_first = (EXTRA && opt.keeps() && nb_tile == 0) ? opt.keep_first : 0;
+  const int n_hpages = min((keep_first + PAGE_TOKENS - 1) / PAGE_TOKENS, p_begin);
+  const int n_bpages = n_hpages > 0 ? n_hpages : (nb_tile + PAGE_TOKENS - 1) / PAGE_TOKENS;
+  const int* btable = (EXTRA && n_bpages > 0 && n_hpages == 0)
+                          ? blocks.block_table + (size_t)slot * blocks.max_pages : nullptr;
   const int n_units = n_bpages + (p_end - p_begin);
 
   auto issue = [&](int unit, int stage) {
-    const bool blk = EXTRA && unit < n_bpages;
-    const int page_id = blk ? btable[unit] : table[p_begin + unit - n_bpages];
+    const bool blk = EXTRA && unit < n_bpages && n_hpages == 0;
+    const int page_id = blk ? btable[unit] : table[unit < n_bpages ? unit : p_begin + unit - n_bpages];
     const bf16* ksrc = (const bf16*)(blk ? blocks.k : kv.k) + ((size_t)page_id * kv.n_kv_heads + kvh) * PAGE_TOKENS * HD;
     const bf16* vsrc = (const bf16*)(blk ? blocks.v : kv.v) + ((size_t)page_id * kv.n_kv_heads + kvh) * PAGE_TOKENS * HD;
     bf16* kdst = kv_s + (size_t)stage * 2 * PAGE_TOKENS * ROW;
@@ -136,7 +146,11 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[n][j] = 0.0f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-  const float sl2 = scale * 1.4426950408889634f;    // scores in units of log2(e)
+  const bool capped = EXTRA && softcap > 0.0f;
+  // scores in units of log2(e); with a cap, first softcap * tanh(scale * score / softcap)
+  const float sl2 = (capped ? 1.0f : scale) * 1.4426950408889634f;
+  const float cap_in = capped ? scale / softcap : 0.0f;
+  auto bent = [&](float raw) { return capped ? nb_softcap(raw, cap_in, softcap) * sl2 : raw * sl2; };
   const int qpos_a = pos0 + q0 + warp * 16 + g;     // absolute position of row g
   const int qpos_b = qpos_a + 8;                    // ... and of row g + 8
   // blocks each of the two rows sees
@@ -145,8 +159,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
 
   for (int u = 0; u < n_units; ++u) {
     const int stage = u & 1;
-    const bool blk = EXTRA && u < n_bpages;
-    const int p = p_begin + u - n_bpages;           // the page of tokens (when not blocks)
+    const bool head = EXTRA && u < n_hpages;        // a page of kept first tokens
+    const bool blk = EXTRA && u < n_bpages && !head;
+    const int p = head ? u : p_begin + u - n_bpages;   // the page of tokens (when not blocks)
     if (u + 1 < n_units) {
       issue(u + 1, stage ^ 1);
       cp_async_wait<1>();
@@ -159,7 +174,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
     // Rows of the last page after the newest key hold whatever an earlier owner of the page
     // left there.  Their probabilities are zero, but zero times a non-finite value is not: the
     // value rows are cleared in the staged copy (masked scores are replaced, not multiplied).
-    const int tail_row = blk ? nb_tile - u * PAGE_TOKENS : last_pos + 1 - p * PAGE_TOKENS;
+    const int tail_row = blk ? nb_tile - u * PAGE_TOKENS : last_pos + 1 - p * PAGE_TOKENS;   // (a head page is full)
     if (tail_row < PAGE_TOKENS) {   // uniform over the CTA
       constexpr int CPR = HD / 8;
       for (int i = tid; i < (PAGE_TOKENS - tail_row) * CPR; i += THREADS) {
@@ -197,17 +212,18 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
         for (int j = 0; j < 4; ++j) {
           const int b = u * PAGE_TOKENS + n * 8 + t * 2 + (j & 1);
           const bool ok = b < ((j < 2) ? nb_a : nb_b);
-          const float v = ok ? sc[n][j] * sl2 : -INFINITY;
+          const float v = ok ? bent(sc[n][j]) : -INFINITY;
           sc[n][j] = v;
           mx[j >> 1] = fmaxf(mx[j >> 1], v);
         }
       }
-    } else if (window <= 0 && j0 + PAGE_TOKENS - 1 <= pos0 + q0 + warp * 16) {
+    } else if (window <= 0 && (!EXTRA || opt.block <= 0) &&
+               j0 + PAGE_TOKENS - 1 <= pos0 + q0 + warp * 16) {
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float v = sc[n][j] * sl2;
+          const float v = EXTRA ? bent(sc[n][j]) : sc[n][j] * sl2;
           sc[n][j] = v;
           mx[j >> 1] = fmaxf(mx[j >> 1], v);
         }
@@ -219,8 +235,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
         for (int j = 0; j < 4; ++j) {
           const int key = j0 + n * 8 + t * 2 + (j & 1);
           const int qp = (j < 2) ? qpos_a : qpos_b;
-          const bool ok = key <= qp && (window <= 0 || key > qp - window);
-          const float v = ok ? sc[n][j] * sl2 : -INFINITY;
+          const bool ok = EXTRA ? (key <= qp && (key >= opt.first_key(qp) || key < keep_first))
+                                : (key <= qp && (window <= 0 || key > qp - window));
+          const float v = ok ? (EXTRA ? bent(sc[n][j]) : sc[n][j] * sl2) : -INFINITY;
           sc[n][j] = v;
           mx[j >> 1] = fmaxf(mx[j >> 1], v);
         }
@@ -291,18 +308,21 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, int q_col,
   const float inv_a = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f;
   const float inv_b = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
   const int ra = warp * 16 + g, rb = ra + 8;
+  // the gate of this head, where the row's sum divides its result
+  const float gi_a = (EXTRA && ra < rows_here) ? inv_a * opt.gate_of(row0 + q0 + ra, h) : inv_a;
+  const float gi_b = (EXTRA && rb < rows_here) ? inv_b * opt.gate_of(row0 + q0 + rb, h) : inv_b;
 #pragma unroll
   for (int n = 0; n < NT; ++n) {
     const int col = h * HD + n * 8 + t * 2;
     if (ra < rows_here) {
       TOut* dst = out + (size_t)(row0 + q0 + ra) * out_stride + col;
-      dst[0] = nb_from_f32<TOut>(o[n][0] * inv_a);
-      dst[1] = nb_from_f32<TOut>(o[n][1] * inv_a);
+      dst[0] = nb_from_f32<TOut>(o[n][0] * gi_a);
+      dst[1] = nb_from_f32<TOut>(o[n][1] * gi_a);
     }
     if (rb < rows_here) {
       TOut* dst = out + (size_t)(row0 + q0 + rb) * out_stride + col;
-      dst[0] = nb_from_f32<TOut>(o[n][2] * inv_b);
-      dst[1] = nb_from_f32<TOut>(o[n][3] * inv_b);
+      dst[0] = nb_from_f32<TOut>(o[n][2] * gi_b);
+      dst[1] = nb_from_f32<TOut>(o[n][3] * gi_b);
     }
   }
 }
@@ -311,7 +331,9 @@ template <int HD, typename TOut, bool EXTRA = false>
 int launch(const void* q, int q_stride, int q_col, const int* cu_rows, const int* seq_slot,
            const int* seq_pos0, const NbPagedKV& kv, int n_heads, void* out, int out_stride,
            float scale, int window, int n_seqs, int max_q_len, cudaStream_t stream,
-           const NbPagedKV& blocks = NbPagedKV{}, int pool = 0, const float* sink = nullptr) {
+           const NbPagedKV& blocks = NbPagedKV{}, int pool = 0, const float* sink = nullptr,
+           const NbAttnOpts* options = nullptr, float softcap = 0.0f) {
+  const NbAttnOpts opt = options ? *options : NbAttnOpts{window, 0, 0, nullptr, 0, 0};
   constexpr int ROW = HD + 8;
   const size_t smem = (size_t)(BLOCK_Q + 4 * PAGE_TOKENS) * ROW * sizeof(bf16);
   auto kern = attention_prefill_kernel<HD, TOut, EXTRA>;
@@ -320,7 +342,7 @@ int launch(const void* q, int q_stride, int q_col, const int* cu_rows, const int
   dim3 grid((max_q_len + BLOCK_Q - 1) / BLOCK_Q, n_heads, n_seqs);
   kern<<<grid, THREADS, smem, stream>>>((const bf16*)q, q_stride, q_col, cu_rows, seq_slot,
                                         seq_pos0, kv, n_heads / kv.n_kv_heads, (TOut*)out,
-                                        out_stride, scale, window, blocks, pool, sink);
+                                        out_stride, scale, window, blocks, pool, sink, opt, softcap);
   return 0;
 }
 
@@ -404,5 +426,47 @@ NB_EXPORT int nb_attention_pooled_mma(const void* q, int q_stride, int q_col, co
 #undef NB_HD
   if (rc) return rc;
   NB_CHECK_LAUNCH("attention_pooled_mma");
+  return 0;
+}
+
+// The same walk under the options of NbAttnOpts (window + kept first tokens, or blocks of
+// positions; a gate per head: fp32 rows with a logit per head at columns gate_col ..), capped
+// scores (softcap > 0) and a sink (fp32 [n_heads] or null): bfloat16 prompts whose heads the
+// tcgen05 kernel does not take.
+NB_EXPORT int nb_attention_prefill_masked(const void* q, int q_stride, int q_col, const int* cu_rows,
+                                          const int* seq_slot, const int* seq_pos0, const void* kc,
+                                          const void* vc, const int* block_table, int max_pages,
+                                          int page, int n_heads, int n_kv_heads, int head_dim,
+                                          const float* sink, void* out, int out_dtype, int out_stride,
+                                          float scale, float softcap, int window, int keep_first,
+                                          int mask_block, const float* gate, int gate_stride,
+                                          int gate_col, int n_seqs, int max_q_len,
+                                          cudaStream_t stream) {
+  if (n_seqs == 0 || max_q_len == 0) return 0;
+  NB_REQUIRE(nb_attention_prefill_supported(NB_BF16, head_dim, n_heads, n_kv_heads, page, q_stride, q_col),
+             NB_ERR_UNSUPPORTED,
+             "attention_prefill_masked: unsupported shape (head size %d, %d/%d heads, row pitch %d)",
+             head_dim, n_heads, n_kv_heads, q_stride);
+  NB_REQUIRE(n_seqs <= 65535 && n_heads <= 65535, NB_ERR_UNSUPPORTED,
+             "attention_prefill_masked: grid too large");
+  NB_REQUIRE((uintptr_t)q % 16 == 0 && window >= 0 && keep_first >= 0 && mask_block >= 0 &&
+                 !(window > 0 && mask_block > 0) && softcap >= 0.0f,
+             NB_ERR_BAD_ARG, "attention_prefill_masked: unaligned queries or a bad mask");
+  NbPagedKV kv{(void*)kc, (void*)vc, block_table, max_pages, page, n_kv_heads, head_dim};
+  const NbAttnOpts opt{window, keep_first, mask_block, gate, gate_stride, gate_col};
+  int rc = NB_ERR_UNSUPPORTED;
+#define NB_CASE(HD_)                                                                                   \
+  case HD_:                                                                                            \
+    rc = out_dtype == NB_F32                                                                           \
+             ? launch<HD_, float, true>(q, q_stride, q_col, cu_rows, seq_slot, seq_pos0, kv, n_heads, out, out_stride, scale, window, n_seqs, max_q_len, stream, NbPagedKV{}, 0, sink, &opt, softcap) \
+             : launch<HD_, bf16, true>(q, q_stride, q_col, cu_rows, seq_slot, seq_pos0, kv, n_heads, out, out_stride, scale, window, n_seqs, max_q_len, stream, NbPagedKV{}, 0, sink, &opt, softcap); \
+    break;
+  switch (head_dim) {
+    NB_CASE(16) NB_CASE(32) NB_CASE(48) NB_CASE(64) NB_CASE(96) NB_CASE(128)
+    default: break;
+  }
+#undef NB_CASE
+  if (rc) return rc;
+  NB_CHECK_LAUNCH("attention_prefill_masked");
   return 0;
 }

@@ -816,6 +816,23 @@ class CudaBackend:
                        layout.n_seqs, layout.max_q_len, max_splits, per_run, _ptr(part),
                        _ptr(counters), 0, 0, 0, self._stream())
             return
+        if shared and q.dtype == torch.bfloat16 and k_store.k.dtype == torch.bfloat16 \
+                and not layout.is_decode and self.use_mma and self.lib.nb_attention_prefill_supported(
+                    code, d, n_heads, k_store.n_kv_heads, k_store.page, q.shape[1], 0):
+            # prompts in bfloat16 with other heads (16, 32, 48, 96; 64 and 128 when tcgen05 is
+            # switched off): mma.sync tiles of 64 rows, the pages of kept first tokens walked
+            # before the window's
+            if layout.n_rows > layout.n_tokens:
+                out[layout.n_tokens:layout.n_rows].zero_()      # padding rows
+            self._call("nb_attention_prefill_masked", _ptr(q), q.shape[1], 0, _ptr(layout.cu_rows),
+                       _ptr(layout.seq_slot), _ptr(layout.seq_pos0), _ptr(k_store.k), _ptr(k_store.v),
+                       _ptr(k_store.block_table), k_store.block_table.shape[1], k_store.page, n_heads,
+                       k_store.n_kv_heads, d, _ptr(sink), _ptr(out), dtype_code(out.dtype),
+                       out.shape[1], float(scale), float(softcap or 0.0), int(window),
+                       int(keep_first), int(chunk), _ptr(gate),
+                       gate.shape[1] if gate is not None else 0, int(gate_col), layout.n_seqs,
+                       layout.max_q_len, self._stream())
+            return
         # any sizes and types, fp32 arithmetic: the 32-bit path, and what the kernels above leave
         v_plane = k_store.v if shared else v_store.k
         self._call("nb_attention_masked", _ptr(q), dtype_code(q.dtype), _ptr(layout.row_slot),

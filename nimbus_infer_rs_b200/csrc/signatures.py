@@ -63,6 +63,7 @@ SIGNATURES = {
     "nb_qkv_norm_rope_append": "piiiippfpifpppippipipiiiiiiiip",
     "nb_pool_blocks": "pppppipppiiiiiiip",
     "nb_attention_pooled_mma": "piippppppipppiiiiippiifiiiip",
+    "nb_attention_prefill_masked": "piippppppiiiiippiiffiiipiiiip",
     "nb_attention_pooled": "pipppppipppiiiiiippifiiip",
     "nb_conv_rope_append": "piipipippppipippippiiiiiiiiiip",
     "nb_conv_act": "piippiipippippiiiip",
