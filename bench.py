@@ -309,7 +309,7 @@ class OpTimer:
              "rms_add", "act_rows", "gather_mul", "qk_norm_rope_append", "pool_blocks",
              "attention_pooled", "delta_rule", "conv_rope_append", "conv_act", "attention_capped",
              "selective_scan", "linear_attention", "rmsnorm_gated", "rms_pair_add", "glu_rows",
-             "cast_cols", "embed_hashed", "last_token", "ln_add", "qkv_norm_rope_append",
+             "cast_cols", "embed_hashed", "ln_add", "qkv_norm_rope_append",
              "attention_masked", "moe_route_sigmoid")
 
     def __init__(self, ops):
@@ -398,7 +398,7 @@ class OpTimer:
         if kind in ("rms_add", "ln_add"):
             return nb(a[0], a[6], a[7]) + 2 * nb(a[3]), 0
         if kind == "embed_hashed":
-            return a[6].numel() * (4 + 2 * a[3].element_size()), 0
+            return a[4].numel() * (4 + 2 * a[1].element_size()), 0
         if kind == "moe_route_sigmoid":
             return nb(a[0]) + 2 * nb(a[12]), 0
         if kind == "qkv_norm_rope_append":

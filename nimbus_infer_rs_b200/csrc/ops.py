@@ -188,28 +188,22 @@ class CudaBackend:
         self._call("nb_embed_pos", _ptr(tokens), _ptr(pos), _ptr(wte), _ptr(wpe),
                    dtype_code(wte.dtype), _ptr(out), n, d, float(scale), self._stream())
 
-    def embed_hashed(self, tokens, pos, row_slot, wte, pair, last, out, scale, mul_prev, mul_cur,
-                     n_buckets):
+    def embed_hashed(self, layout, wte, pair, last, out, scale, mul_prev, mul_cur, n_buckets):
         """``out[r] = scale * wte[token] + pair[(prev * mul_prev + token * mul_cur) % n_buckets]``
         (row ``n_buckets`` of ``pair`` for a sequence's first token); ``prev`` is the row before
-        in the step or, at the start of a continued sequence, ``last[slot, 0]`` (fp32 state)."""
-        _check(tokens, "tokens", torch.int32, 1)
+        in the step or, at the start of a continued sequence, ``last[slot, 0]`` (fp32 state),
+        which then takes the token of the sequence's last row in this step."""
         _check(wte, "wte", None, 2)
         _check(pair, "pair", wte.dtype, 2)
         _check(last, "last", torch.float32, 2)
         _check(out, "out", torch.float32, 2)
         n, d = out.shape
-        if tokens.numel() < n or wte.shape[1] != d or pair.shape != (n_buckets + 1, d):
+        if layout.tokens.numel() < n or wte.shape[1] != d or pair.shape != (n_buckets + 1, d):
             raise KernelError("embed_hashed: shapes do not agree")
-        self._call("nb_embed_hashed", _ptr(tokens), _ptr(pos), _ptr(row_slot), _ptr(wte), _ptr(pair),
-                   dtype_code(wte.dtype), _ptr(last), last.stride(0), _ptr(out), n, d, float(scale),
-                   int(mul_prev), int(mul_cur), int(n_buckets), self._stream())
-
-    def last_token(self, tokens, pos, row_slot, last, n_rows):
-        """``last[slot, 0]`` = the token of each sequence's last row in this step."""
-        _check(last, "last", torch.float32, 2)
-        self._call("nb_last_token", _ptr(tokens), _ptr(pos), _ptr(row_slot), _ptr(last),
-                   last.stride(0), int(n_rows), self._stream())
+        self._call("nb_embed_hashed", _ptr(layout.tokens), _ptr(layout.row_pos), _ptr(layout.row_slot),
+                   _ptr(layout.cu_rows), layout.n_seqs, _ptr(wte), _ptr(pair), dtype_code(wte.dtype),
+                   _ptr(last), last.stride(0), _ptr(out), n, d, float(scale), int(mul_prev),
+                   int(mul_cur), int(n_buckets), self._stream())
 
     def layernorm(self, x, gamma, beta, eps, out, rows=None):
         _check(x, "x", torch.float32, 2)

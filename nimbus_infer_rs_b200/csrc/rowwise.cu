@@ -109,18 +109,30 @@ NB_EXPORT int nb_embed_pos(const int* tokens, const int* pos, const void* wte, c
 // x[r] = scale * wte[token[r]] + pair[bucket(r)], fp32 result: a second table indexed by a hash
 // of (previous token, token):  bucket = (prev * mul_prev + token * mul_cur) mod n_buckets, and
 // row n_buckets (the table's last) for a sequence's first token.  The previous token of a row is
-// the row before it in the step, or, for the first row of a continued sequence, what the
-// sequence's state row holds (`last`, one float per slot: token ids are exact there).
-// `last` is only read here; nb_last_token writes it once every row has been embedded.
+// the row before it in the step or, for the first row of a continued sequence, what the
+// sequence's state row holds (`last`, one float per slot: token ids are exact there); the state
+// row then takes the token of the sequence's last row in this step.
+//
+// The grid is one CTA per row and one more per sequence.  A sequence's first row in the step is
+// left to the sequence's CTA, which reads the state row, embeds that row, and only then (behind
+// a barrier of the CTA) writes the state row: no other CTA reads it.
 // ---------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_hashed_kernel(const int* tokens, const int* pos, const int* row_slot,
-                                    const T* __restrict__ wte, const T* __restrict__ pair,
-                                    const float* last, int last_stride, float* out, int d,
-                                    float scale, int mul_prev, int mul_cur, int n_buckets) {
+                                    const int* cu_rows, int n_rows, const T* __restrict__ wte,
+                                    const T* __restrict__ pair, float* last, int last_stride,
+                                    float* out, int d, float scale, int mul_prev, int mul_cur,
+                                    int n_buckets) {
   nb_grid_dependency_wait();
   nb_launch_dependents();
-  const int r = blockIdx.x;
+  const bool of_sequence = (int)blockIdx.x >= n_rows;
+  int r = blockIdx.x, last_row = -1;
+  if (of_sequence) {
+    const int s = blockIdx.x - n_rows;
+    r = cu_rows[s];
+    last_row = cu_rows[s + 1] - 1;
+    if (last_row < r) return;                 // a sequence without rows
+  }
   const int tok = tokens[r];
   float* o = out + (size_t)r * d;
   const int slot = row_slot[r];
@@ -129,11 +141,11 @@ __global__ void embed_hashed_kernel(const int* tokens, const int* pos, const int
     return;
   }
   const int p = pos[r];
+  const bool first_in_step = !(r > 0 && row_slot[r - 1] == slot && pos[r - 1] == p - 1);
+  if (first_in_step != of_sequence) return;   // the other kind of CTA has this row
   long long bucket = n_buckets;
   if (p > 0) {
-    int prev;
-    if (r > 0 && row_slot[r - 1] == slot && pos[r - 1] == p - 1) prev = tokens[r - 1];
-    else prev = (int)last[(size_t)slot * last_stride];
+    const int prev = of_sequence ? (int)last[(size_t)slot * last_stride] : tokens[r - 1];
     bucket = ((long long)prev * mul_prev + (long long)tok * mul_cur) % n_buckets;
     if (bucket < 0) bucket += n_buckets;
   }
@@ -141,51 +153,34 @@ __global__ void embed_hashed_kernel(const int* tokens, const int* pos, const int
   const T* b = pair + (size_t)bucket * d;
   for (int i = threadIdx.x; i < d; i += blockDim.x)
     o[i] = nb_to_f32(e[i]) * scale + nb_to_f32(b[i]);
+  if (of_sequence) {
+    __syncthreads();                          // every thread has read the state row
+    if (threadIdx.x == 0 && tokens[last_row] >= 0)
+      last[(size_t)slot * last_stride] = (float)tokens[last_row];
+  }
 }
 
-// last[slot] = token of the sequence's last row in this step (a row whose successor is not the
-// same sequence's next token).
-__global__ void last_token_kernel(const int* tokens, const int* pos, const int* row_slot,
-                                  float* last, int last_stride, int n_rows) {
-  nb_grid_dependency_wait();
-  nb_launch_dependents();
-  const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= n_rows) return;
-  const int slot = row_slot[r];
-  if (slot < 0 || tokens[r] < 0) return;
-  const bool more = r + 1 < n_rows && row_slot[r + 1] == slot && pos[r + 1] == pos[r] + 1;
-  if (!more) last[(size_t)slot * last_stride] = (float)tokens[r];
-}
-
-NB_EXPORT int nb_embed_hashed(const int* tokens, const int* pos, const int* row_slot, const void* wte,
-                              const void* pair, int table_dtype, const float* last, int last_stride,
-                              float* out, int n_rows, int d, float scale, int mul_prev, int mul_cur,
-                              int n_buckets, cudaStream_t stream) {
+NB_EXPORT int nb_embed_hashed(const int* tokens, const int* pos, const int* row_slot,
+                              const int* cu_rows, int n_seqs, const void* wte, const void* pair,
+                              int table_dtype, float* last, int last_stride, float* out, int n_rows,
+                              int d, float scale, int mul_prev, int mul_cur, int n_buckets,
+                              cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  NB_REQUIRE(n_rows > 0 && d > 0 && n_buckets > 0 && last != nullptr, NB_ERR_BAD_ARG,
-             "embed_hashed: bad sizes rows=%d d=%d buckets=%d", n_rows, d, n_buckets);
+  NB_REQUIRE(n_rows > 0 && n_seqs >= 0 && d > 0 && n_buckets > 0 && last != nullptr && cu_rows != nullptr,
+             NB_ERR_BAD_ARG, "embed_hashed: bad sizes rows=%d d=%d buckets=%d", n_rows, d, n_buckets);
   const int threads = d >= 256 ? 256 : (d >= 128 ? 128 : 64);
+  const dim3 grid(n_rows + n_seqs);
   if (table_dtype == NB_F32)
-    NB_CUDA(nb_launch(embed_hashed_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, tokens, pos,
-                      row_slot, (const float*)wte, (const float*)pair, last, last_stride, out, d,
-                      scale, mul_prev, mul_cur, n_buckets));
+    NB_CUDA(nb_launch(embed_hashed_kernel<float>, grid, dim3(threads), 0, stream, tokens, pos,
+                      row_slot, cu_rows, n_rows, (const float*)wte, (const float*)pair, last,
+                      last_stride, out, d, scale, mul_prev, mul_cur, n_buckets));
   else if (table_dtype == NB_BF16)
-    NB_CUDA(nb_launch(embed_hashed_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream,
-                      tokens, pos, row_slot, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)pair,
+    NB_CUDA(nb_launch(embed_hashed_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, tokens, pos,
+                      row_slot, cu_rows, n_rows, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)pair,
                       last, last_stride, out, d, scale, mul_prev, mul_cur, n_buckets));
   else
     NB_REQUIRE(false, NB_ERR_BAD_ARG, "embed_hashed: unknown table dtype %d", table_dtype);
   NB_CHECK_LAUNCH("embed_hashed");
-  return 0;
-}
-
-NB_EXPORT int nb_last_token(const int* tokens, const int* pos, const int* row_slot, float* last,
-                            int last_stride, int n_rows, cudaStream_t stream) {
-  if (n_rows == 0) return 0;
-  NB_REQUIRE(n_rows > 0 && last != nullptr && last_stride > 0, NB_ERR_BAD_ARG, "last_token: bad sizes");
-  NB_CUDA(nb_launch(last_token_kernel, dim3((n_rows + 127) / 128), dim3(128), 0, stream, tokens, pos,
-                    row_slot, last, last_stride, n_rows));
-  NB_CHECK_LAUNCH("last_token");
   return 0;
 }
 

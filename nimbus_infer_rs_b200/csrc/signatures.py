@@ -53,8 +53,7 @@ SIGNATURES = {
     "nb_set_overlap": "i",
     "nb_get_overlap": "",
     "nb_embed_pos": "ppppipiifp",
-    "nb_embed_hashed": "pppppipipiifiiip",
-    "nb_last_token": "ppppiip",
+    "nb_embed_hashed": "ppppippipipiifiiip",
     "nb_ln_add": "ppfppfppiiip",
     "nb_rms_add": "ppfppfppiiip",
     "nb_act_rows": "piiippiiip",

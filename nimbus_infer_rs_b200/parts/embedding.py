@@ -41,8 +41,8 @@ class HashedPairEmbedding(TokenEmbedding):
     takes the table's last row (row ``buckets``).
 
     The token before a step's first one belongs to the sequence's state: one number per slot in
-    the sequence's state row (token ids are whole numbers below 2^24, exact in fp32), written
-    after the step's rows have been embedded."""
+    the sequence's state row (token ids are whole numbers below 2^24, exact in fp32), written by
+    the same kernel once the sequence's first row of the step has read it."""
     kind = "hashed_pair_embedding"
 
     def __init__(self, vocab_size: int, width: int, buckets: int, mul_prev: int, mul_cur: int,
@@ -67,9 +67,8 @@ class HashedPairEmbedding(TokenEmbedding):
             raise ValueError("a hashed pair embedding does not add a position table")
         lay = ctx.layout
         x = torch.empty((lay.n_rows, self.width), device=self.table.device, dtype=torch.float32)
-        ctx.ops.embed_hashed(lay.tokens, lay.row_pos, lay.row_slot, self.table, self.pair_table,
-                             ctx.state, x, self.scale, self.mul_prev, self.mul_cur, self.buckets)
-        ctx.ops.last_token(lay.tokens, lay.row_pos, lay.row_slot, ctx.state, lay.n_rows)
+        ctx.ops.embed_hashed(lay, self.table, self.pair_table, ctx.state, x, self.scale,
+                             self.mul_prev, self.mul_cur, self.buckets)
         return x
 
 

@@ -25,8 +25,9 @@ class CpuBackend:
             x = x + wpe[pos[:n].long()].float()
         out.copy_(torch.where(valid[:, None], x, torch.zeros_like(x)))
 
-    def embed_hashed(self, tokens, pos, row_slot, wte, pair, last, out, scale, mul_prev, mul_cur,
-                     n_buckets):
+    def embed_hashed(self, layout, wte, pair, last, out, scale, mul_prev, mul_cur, n_buckets):
+        tokens, pos, row_slot = layout.tokens, layout.row_pos, layout.row_slot
+        before = last.clone()
         for r in range(out.shape[0]):
             tok, slot, p = int(tokens[r]), int(row_slot[r]), int(pos[r])
             if tok < 0 or slot < 0:
@@ -37,18 +38,12 @@ class CpuBackend:
                 if r > 0 and int(row_slot[r - 1]) == slot and int(pos[r - 1]) == p - 1:
                     prev = int(tokens[r - 1])
                 else:
-                    prev = int(last[slot, 0])
+                    prev = int(before[slot, 0])
                 bucket = (prev * mul_prev + tok * mul_cur) % n_buckets
             out[r] = wte[tok].float() * scale + pair[bucket].float()
-
-    def last_token(self, tokens, pos, row_slot, last, n_rows):
-        for r in range(n_rows):
-            slot = int(row_slot[r])
-            if slot < 0 or int(tokens[r]) < 0:
-                continue
-            more = r + 1 < n_rows and int(row_slot[r + 1]) == slot and int(pos[r + 1]) == int(pos[r]) + 1
+            more = r + 1 < out.shape[0] and int(row_slot[r + 1]) == slot and int(pos[r + 1]) == p + 1
             if not more:
-                last[slot, 0] = float(int(tokens[r]))
+                last[slot, 0] = float(tok)
 
     def ln_add(self, y, gamma, eps, residual, next_gamma, next_eps, out_next, out_cast):
         def unit(t, e):

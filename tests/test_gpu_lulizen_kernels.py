@@ -94,9 +94,7 @@ def test_hashed_pairs_across_portions_and_slots_used_again(ops, table):
         entries = [(s, seqs[s][at[s]:at[s] + n], []) for s, n in step.items()]
         lay = build_layout(entries, [at[s] for s in step], torch.device(DEV), pad_rows_to=4)
         out = torch.full((lay.n_rows, D), 9.0, device=DEV)
-        ops.embed_hashed(lay.tokens, lay.row_pos, lay.row_slot, wte.to(DEV), pair.to(DEV), last, out,
-                         1.0, a, b, B)
-        ops.last_token(lay.tokens, lay.row_pos, lay.row_slot, last, lay.n_rows)
+        ops.embed_hashed(lay, wte.to(DEV), pair.to(DEV), last, out, 1.0, a, b, B)
         r = 0
         for s, n in step.items():
             got[s].append(out[r:r + n].cpu())
